@@ -33,12 +33,14 @@ def registered_architectures() -> list:
 
 
 def resolve_architecture(config: dict) -> Architecture:
-    """Chosen by config.json's `architectures[0]`, else by `model_type`."""
+    """Chosen by config.json's `architectures[0]` (or `architecture`, a single name), else by `model_type`."""
     names = list(config.get("architectures") or [])
+    if isinstance(config.get("architecture"), str):
+        names.append(config["architecture"])
     if config.get("model_type"):
         names.append(config["model_type"])
     if not names:
-        raise ConfigError("config.json names no architecture (keys 'architectures' or 'model_type'); "
+        raise ConfigError("config.json names no architecture (keys 'architectures', 'architecture' or 'model_type'); "
                           f"registered: {', '.join(registered_architectures())}")
     for n in names:
         if n in _ARCHITECTURES:

@@ -23,7 +23,7 @@ using bf16 = __nv_bfloat16;
 template <class TW>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int vocab, const int32_t* __restrict__ slots,
-                             const int32_t* __restrict__ sampled) {
+                             const int32_t* __restrict__ sampled, float* __restrict__ copy) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int row = blockIdx.x;
@@ -32,7 +32,13 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __res
   const bool ok = tok >= 0 && tok < vocab;
   const TW* src = table + static_cast<int64_t>(ok ? tok : 0) * H;
   float* dst = out + static_cast<int64_t>(row) * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? sb::widen(src[i]) : 0.0f;
+  // `copy`: a second place for the same rows, for models whose later layers read the embedding again
+  float* dst2 = copy != nullptr ? copy + static_cast<int64_t>(row) * H : nullptr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = ok ? sb::widen(src[i]) : 0.0f;
+    dst[i] = v;
+    if (dst2 != nullptr) dst2[i] = v;
+  }
 }
 
 __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
@@ -56,6 +62,8 @@ struct RopeAppendParams {
   int64_t head_stride;  // elements between kv heads (= page_size * D)
   int Hq, Hkv, D;
   int write_kv;
+  int v_from_k;         // 1: no value projection; a value head is its key head as projected (before rotation), and a qkv row
+                        // holds (Hq + Hkv) D elements
 };
 
 // One thread per (head, rotation pair) of a token; blockIdx.y walks the token's pairs.
@@ -69,7 +77,7 @@ __global__ void rope_append_kernel(RopeAppendParams p) {
   if (item >= heads * half) return;
   const int pos = p.positions[row];
   const int slot = p.slots[row];
-  const int width = heads * D;
+  const int width = (p.v_from_k ? p.Hq + p.Hkv : heads) * D;
   const int head = item / half, j = item % half;
   int d0, d1;
   if (j < rh) {
@@ -91,7 +99,7 @@ __global__ void rope_append_kernel(RopeAppendParams p) {
   if (p.write_kv && head >= p.Hq) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
   // positions, slots, the block table and the cos/sin table are inputs of the step; only qkv comes from the kernel before
   sb::grid_dependency_wait();
-  const float* src = p.qkv + static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
+  const float* src = p.qkv + static_cast<int64_t>(row) * width + static_cast<int64_t>(is_v && p.v_from_k ? head - p.Hkv : head) * D;
   // the K ranges' sums are added in ascending order; up to kInFlight of them are requested at once (each is a round
   // trip to L2, and with few tokens those are what this kernel's time consists of)
   constexpr int kInFlight = 8;
@@ -175,7 +183,8 @@ __global__ void rope_append_vec_kernel(RopeAppendParams p) {
     c23 = cs[1];
   }
   sb::grid_dependency_wait();   // everything above is an input of the step; qkv comes from the kernel before
-  const float* src = p.qkv + static_cast<int64_t>(row) * heads * D + static_cast<int64_t>(head) * D;
+  const float* src = p.qkv + static_cast<int64_t>(row) * (p.v_from_k ? p.Hq + p.Hkv : heads) * D +
+                     static_cast<int64_t>(is_v && p.v_from_k ? head - p.Hkv : head) * D;
   // the K ranges' sums are added in ascending order; up to kInFlight of them are requested at once
   constexpr int kInFlight = 8;
   float4 pa[kInFlight], pb[kInFlight];
@@ -223,8 +232,9 @@ __global__ void rope_append_vec_kernel(RopeAppendParams p) {
 }
 
 // ------------------------------------------------------------------ swiglu
+// act 0: silu(a) = a / (1 + e^-a); act 1: the tanh form of gelu, 0.5 a (1 + tanh(sqrt(2/pi) (a + 0.044715 a^3)))
 template <class TO>
-__global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int n, int I) {
+__global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int n, int I, int act) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int64_t total = static_cast<int64_t>(n) * I;
@@ -232,7 +242,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict_
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / I, c = i % I;
     const float a = gate_up[r * 2 * I + c], b = gate_up[r * 2 * I + I + c];
-    out[i] = sb::narrow<TO>((a / (1.0f + expf(-a))) * b);
+    const float g = act == 1 ? 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a))) : a / (1.0f + expf(-a));
+    out[i] = sb::narrow<TO>(g * b);
   }
 }
 
@@ -263,17 +274,51 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __
   }
 }
 
+// ------------------------------------------------------------------ two streams side by side
+// out[r] = [a[r] (+ partial sums, ascending); b[r]] as one row of 2 H elements: the input of a projection that reads the
+// residual stream and a second stream of the same width together.
+template <class TO>
+__global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ partials, int n_partials,
+                                   int64_t partial_stride, const float* __restrict__ b, TO* __restrict__ out, int H) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t r = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = a[r * H + i];
+    if (n_partials > 0) {
+      const float* p = partials + r * H + i;
+      float sum = p[0];
+      for (int s = 1; s < n_partials; ++s) sum += p[s * partial_stride];
+      v += sum;
+    }
+    out[r * 2 * H + i] = sb::narrow<TO>(v);
+    out[r * 2 * H + H + i] = sb::narrow<TO>(b[r * H + i]);
+  }
+}
+
 }  // namespace
 
 // dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
 
+SB_EXPORT int sb_concat_rows(const float* a, const float* partials, int n_partials, int64_t partial_stride, const float* b,
+                             void* out, int out_dtype, int n, int H, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (out_dtype == 0)
+    sb::launch_pdl(concat_rows_kernel<float>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<float*>(out), H);
+  else if (out_dtype == 1)
+    sb::launch_pdl(concat_rows_kernel<bf16>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<bf16*>(out), H);
+  else
+    return sb::fail("sb_concat_rows: unsupported out dtype %d", out_dtype);
+  return sb::check_launch("sb_concat_rows");
+}
+
 SB_EXPORT int sb_embed(const int32_t* tokens, const void* table, int table_dtype, float* out, int n, int H, int vocab,
-                       const int32_t* slots, const int32_t* sampled, cudaStream_t stream) {
+                       const int32_t* slots, const int32_t* sampled, float* copy, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (table_dtype == 0)
-    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab, slots, sampled);
+    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab, slots, sampled, copy);
   else if (table_dtype == 1)
-    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab, slots, sampled);
+    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab, slots, sampled, copy);
   else
     return sb::fail("sb_embed: unsupported table dtype %d", table_dtype);
   return sb::check_launch("sb_embed");
@@ -283,13 +328,13 @@ SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_s
                              const int32_t* slots, const float* cos_sin, int rotary_dim, void* q_out, int q_dtype,
                              void* k_base, int kv_dtype, const int32_t* block_table, int max_pages, int page_size,
                              int64_t page_stride, int64_t v_offset, int64_t head_stride, int n, int Hq, int Hkv, int D,
-                             int write_kv, cudaStream_t stream) {
+                             int write_kv, int v_from_k, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (D % 2 != 0 || rotary_dim % 2 != 0 || rotary_dim > D || rotary_dim < 0)
     return sb::fail("sb_rope_append: head_dim %d / rotary_dim %d must be even and rotary_dim <= head_dim", D, rotary_dim);
   if (n_partials < 1) return sb::fail("sb_rope_append: n_partials must be >= 1");
   RopeAppendParams p{qkv, n_partials, partial_stride, positions, slots, cos_sin, rotary_dim, q_out, k_base,
-                     block_table, max_pages, page_size, page_stride, v_offset, head_stride, Hq, Hkv, D, write_kv};
+                     block_table, max_pages, page_size, page_stride, v_offset, head_stride, Hq, Hkv, D, write_kv, v_from_k};
   const int threads = 128;
   const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_base) |
                          reinterpret_cast<uintptr_t>(cos_sin)) & 15) == 0;
@@ -312,12 +357,12 @@ SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_s
   return sb::check_launch("sb_rope_append");
 }
 
-SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, int I, cudaStream_t stream) {
+SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, int I, int act, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int64_t total = static_cast<int64_t>(n) * I;
   const int blocks = static_cast<int>((total + 255) / 256 < sb::sm_count() * 16 ? (total + 255) / 256 : sb::sm_count() * 16);
-  if (out_dtype == 0) sb::launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, static_cast<float*>(out), n, I);
-  else if (out_dtype == 1) sb::launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, gate_up, static_cast<bf16*>(out), n, I);
+  if (out_dtype == 0) sb::launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, static_cast<float*>(out), n, I, act);
+  else if (out_dtype == 1) sb::launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, gate_up, static_cast<bf16*>(out), n, I, act);
   else return sb::fail("sb_swiglu: unsupported out dtype %d", out_dtype);
   return sb::check_launch("sb_swiglu");
 }
@@ -330,17 +375,19 @@ SB_EXPORT int sb_gather_rows(const float* in, const float* partials, int n_parti
 }
 
 // ------------------------------------------------------------------ operations of the native step program (step_ops.h)
-// i: 0 table, 1 table dtype, 2 out (float32 [n, H]), 3 H, 4 vocab, 5 the table of last sampled tokens (or 0)
+// i: 0 table, 1 table dtype, 2 out (float32 [n, H]), 3 H, 4 vocab, 5 the table of last sampled tokens (or 0),
+//    6 a second buffer [n, H] that receives the same rows (or 0)
 SB_EXPORT int sb_op_embed(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   const int32_t* sampled = ptr<const int32_t>(op->i[5]);
   return sb_embed(tokens(s), ptr<const void>(op->i[0]), (int)op->i[1], ptr<float>(op->i[2]), s->n, (int)op->i[3], (int)op->i[4],
-                  sampled ? slots(s) : nullptr, sampled, static_cast<cudaStream_t>(stream));
+                  sampled ? slots(s) : nullptr, sampled, ptr<float>(op->i[6]), static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 qkv partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 cos_sin, 5 rotary_dim,
 //    6 q_out, 7 q dtype, 8 cache layer, 9 cache dtype, 10 block table, 11 pages per sequence, 12 page size,
-//    13 page stride, 14 v offset, 15 head stride, 16 Hq, 17 Hkv, 18 D, 19 write_kv, 20 tile plan (-1: none)
+//    13 page stride, 14 v offset, 15 head stride, 16 Hq, 17 Hkv, 18 D, 19 write_kv, 20 tile plan (-1: none),
+//    21 values are the unrotated keys (the rows of qkv hold q and k only)
 SB_EXPORT int sb_op_rope_append(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (op->i[20] >= 0 && s->plan[op->i[20]].fused) return SB_OP_SKIPPED;     // the decode kernel rotates and appends itself
@@ -348,13 +395,13 @@ SB_EXPORT int sb_op_rope_append(const SbOp* op, const SbStep* s, void* stream) {
   return sb_rope_append(ptr<const float>(op->i[0]), P, static_cast<int64_t>(s->n) * op->i[1], positions(s), slots(s),
                         ptr<const float>(op->i[4]), (int)op->i[5], ptr<void>(op->i[6]), (int)op->i[7], ptr<void>(op->i[8]), (int)op->i[9],
                         ptr<const int32_t>(op->i[10]), (int)op->i[11], (int)op->i[12], op->i[13], op->i[14], op->i[15], s->n,
-                        (int)op->i[16], (int)op->i[17], (int)op->i[18], (int)op->i[19], static_cast<cudaStream_t>(stream));
+                        (int)op->i[16], (int)op->i[17], (int)op->i[18], (int)op->i[19], (int)op->i[21], static_cast<cudaStream_t>(stream));
 }
 
-// i: 0 gate_up (float32 [n, 2 I]), 1 out, 2 out dtype, 3 I
+// i: 0 gate_up (float32 [n, 2 I]), 1 out, 2 out dtype, 3 I, 4 the gate's activation (0 silu, 1 tanh form of gelu)
 SB_EXPORT int sb_op_swiglu(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
-  return sb_swiglu(ptr<const float>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], s->n, (int)op->i[3], static_cast<cudaStream_t>(stream));
+  return sb_swiglu(ptr<const float>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], s->n, (int)op->i[3], (int)op->i[4], static_cast<cudaStream_t>(stream));
 }
 
 // The rows whose logits are wanted, with the pending partial sums of the last projection added.
@@ -366,4 +413,14 @@ SB_EXPORT int sb_op_gather_rows(const SbOp* op, const SbStep* s, void* stream) {
   const int P = partials ? partial_count(op->i[2], op->i[3], s->n) : 0;
   return sb_gather_rows(ptr<const float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[5], wanted_rows(s), ptr<float>(op->i[4]),
                         s->wanted, (int)op->i[5], static_cast<cudaStream_t>(stream));
+}
+
+// i: 0 a (float32 [n, H]), 1 pending partial sums on a (flat; 0: none), 2 K ranges S, 3 most tokens with a buffer per range,
+//    4 b (float32 [n, H]), 5 out [n, 2 H], 6 out dtype, 7 H
+SB_EXPORT int sb_op_concat_rows(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const float* partials = ptr<const float>(op->i[1]);
+  const int P = partials ? partial_count(op->i[2], op->i[3], s->n) : 0;
+  return sb_concat_rows(ptr<const float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[7], ptr<const float>(op->i[4]),
+                        ptr<void>(op->i[5]), (int)op->i[6], s->n, (int)op->i[7], static_cast<cudaStream_t>(stream));
 }

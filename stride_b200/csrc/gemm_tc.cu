@@ -69,6 +69,7 @@ struct GemmParams {
   int kblocks_per_split;
   int tiles_m, tiles_n, splits;
   int half_rows;         // kSwiglu: rows of the gate half (intermediate size); W is [2 * half_rows, K]
+  int gate_act;          // kSwiglu: the gate's activation (sb::gemm_tile::GateAct)
   int* status;
 };
 
@@ -189,7 +190,7 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int n0 = tile_n * BN;
     if (EPI == kSwiglu) {
       float* xch = reinterpret_cast<float*>(smem_raw + ((smem0 - smem_u32(smem_raw))));  // stage 0 is free by now
-      swiglu_tile(tmem_base, xch, reinterpret_cast<bf16*>(p.out), p.ldo, tile_m, p.half_rows, n0, p.N, BN, quarter, lane, ok);
+      swiglu_tile(tmem_base, xch, reinterpret_cast<bf16*>(p.out), p.ldo, tile_m, p.half_rows, n0, p.N, BN, quarter, lane, ok, p.gate_act);
     } else {
       store_tile<EPI>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), p.out + static_cast<int64_t>(split) * p.split_stride,
                       tile_m * kTileM + quarter * 32 + lane, p.M, n0, p.N, p.ldo, BN, ok);
@@ -358,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               if (n < p.N) {
                 const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
                 const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(gate_act(g, p.gate_act) * u);
               }
             }
           }
@@ -672,7 +673,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               if (n < p.N) {
                 const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
                 const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(gate_act(g, p.gate_act) * u);
               }
             }
           }
@@ -837,7 +838,7 @@ gemm_tc_wide_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             const int n = tile_n * BN + c0 + c;
-            if (n < p.N) out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g[c]) * u[c]);
+            if (n < p.N) out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(gate_act(g[c], p.gate_act) * u[c]);
           }
         }
       }
@@ -892,6 +893,7 @@ SB_EXPORT int sb_gemm_tc_partial_tokens() { return 512; }
 //               order; with more tokens the kernel adds them itself and stores the sum at out.
 //   epilogue 1: out float32 [n, ldo] += result (one range)
 //   epilogue 2: W is [2 * half_rows, K] (gate rows then up rows); out bfloat16 [n, ldo] = silu(gate) * up
+//   epilogue 3: the same with the tanh form of gelu as the gate's activation
 SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int n, int M, int K,
                          int epilogue, int splits, int64_t split_stride, int half_rows, cudaStream_t stream) {
   if (n <= 0 || M <= 0) return 0;
@@ -899,7 +901,9 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     return sb::fail("sb_gemm_tc: K %d and the leading dimensions (%lld, %lld) must be multiples of 8", K, (long long)ldx, (long long)ldw);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
     return sb::fail("sb_gemm_tc: operands must be 16-byte aligned");
-  if (epilogue < 0 || epilogue > 2) return sb::fail("sb_gemm_tc: unknown epilogue %d", epilogue);
+  if (epilogue < 0 || epilogue > 3) return sb::fail("sb_gemm_tc: unknown epilogue %d", epilogue);
+  const int gate = epilogue == 3 ? kGateGeluTanh : kGateSilu;
+  if (epilogue == 3) epilogue = kSwiglu;
   const bool fold = splits > 1 && n > sb_gemm_tc_partial_tokens();   // the kernel adds the ranges
   if (epilogue == kSwiglu && splits != 1) return sb::fail("sb_gemm_tc: the SwiGLU epilogue takes no K ranges");
   if (epilogue == kAdd && splits != 1) return sb::fail("sb_gemm_tc: the sum of K ranges is added to the residual by its consumer (plain store)");
@@ -962,6 +966,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   // four, 0.940 with three).
   if (n <= 128) p.stages = max(2, min(p.stages, min(6, p.kblocks_per_split)));
   p.half_rows = half_rows;
+  p.gate_act = gate;
   p.status = status;
 
   // The SwiGLU product of many tokens runs on pairs of CTAs or with two weight tiles a CTA; both bring the same bytes
@@ -1156,7 +1161,7 @@ SB_EXPORT int sb_gemm_tc_status() {
 // i: 0 x (bfloat16 [n, ldx]), 1 ldx, 2 weight, 3 ldw, 4 out, 5 M, 6 K,
 //    7 mode: 0 = out float32 [n, M], K in one range; 1 = partial sums [P, n, M] of the weight's K ranges (P = S up to
 //            sb_gemm_tc_partial_tokens() tokens, else 1: the kernel adds the ranges); 2 = out float32 [n, M] += result;
-//            3 = SwiGLU, out bfloat16 [n, M / 2]
+//            3 = SwiGLU, out bfloat16 [n, M / 2]; 4 = the same with the tanh form of gelu on the gate
 //    8 K ranges S (mode 1), 9 rows: 0 = the step's tokens, 1 = the rows whose logits are wanted
 SB_EXPORT int sb_op_linear_tc(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
@@ -1175,6 +1180,7 @@ SB_EXPORT int sb_op_linear_tc(const SbOp* op, const SbStep* s, void* stream) {
     }
     case 2: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M, n, M, K, kAdd, 1, 0, 0, st);
     case 3: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M / 2, n, M, K, kSwiglu, 1, 0, M / 2, st);
+    case 4: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M / 2, n, M, K, 3, 1, 0, M / 2, st);
     default: return sb::fail("sb_op_linear_tc: unknown mode %d", mode);
   }
 }

@@ -46,6 +46,18 @@ __device__ __forceinline__ uint32_t instr_desc(int n) { return sb::tc5::instr_de
 // file, so that a token's product has the same bits from each.
 __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
+// The activation of the gate half of a gated feed-forward: 0 = silu, 1 = the tanh form of gelu,
+// 0.5 g (1 + tanh(y)) with y = sqrt(2/pi) (g + 0.044715 g^3), which is g / (1 + e^(-2y)): the same two approximated
+// instructions as silu. The exponent is capped so that the divisor stays where the approximated division is defined.
+enum GateAct { kGateSilu = 0, kGateGeluTanh = 1 };
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == kGateGeluTanh) {
+    const float y = 0.7978845608028654f * fmaf(0.044715f * g, g * g, g);
+    return __fdividef(g, 1.0f + __expf(fminf(-2.0f * y, 80.0f)));
+  }
+  return silu_fast(g);
+}
+
 // Rows of one accumulator tile to global memory: out[n, m] = d (kStore) or out[n, m] += d (kAdd). Each thread
 // owns output feature m and walks the tile's tokens sixteen at a time; for kAdd the residual values of the
 // next sixteen are requested before the current sixteen are summed and stored.
@@ -82,7 +94,7 @@ __device__ __forceinline__ void store_tile(uint32_t tmem_row, float* out, int m,
 // bfloat16, j = tile_m * 64 + row. `quarter` = warp % 4 (the TMEM lanes this warp may read), xch: 16 x 64 floats of
 // shared memory that nothing else uses meanwhile.
 __device__ __forceinline__ void swiglu_tile(uint32_t tmem_base, float* xch, bf16* out, int64_t ldo, int tile_m, int half_rows, int n0,
-                                            int N, int BN, int quarter, int lane, bool ok) {
+                                            int N, int BN, int quarter, int lane, bool ok, int act = kGateSilu) {
   const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
   for (int c0 = 0; c0 < BN; c0 += 16) {
     float v[16];
@@ -104,7 +116,7 @@ __device__ __forceinline__ void swiglu_tile(uint32_t tmem_base, float* xch, bf16
         if (n < N) {
           const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
           const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-          out[static_cast<int64_t>(n) * ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
+          out[static_cast<int64_t>(n) * ldo + j] = __float2bfloat16_rn(gate_act(g, act) * u);
         }
       }
     }

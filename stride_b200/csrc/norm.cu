@@ -185,7 +185,76 @@ __global__ void __launch_bounds__(64) rmsnorm_rows_kernel(float* __restrict__ h,
   }
 }
 
+// ------------------------------------------------------------------ layer norm
+// One block per row: x = h + (partial_0 + partial_1 + ...) as in rmsnorm_kernel (written back to h when partials are
+// given); mean = sum(x) / H; var = sum((x - mean)^2) / H, the deviations taken from the row kept in shared memory;
+// out = (x - mean) / sqrt(var + eps) * w + b. Both sums in the order of sb::block_sum, which the width alone decides.
+template <class TW, class TO>
+__global__ void __launch_bounds__(1024) layernorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
+                                                         int64_t partial_stride, const TW* __restrict__ weight,
+                                                         const TW* __restrict__ bias, TO* __restrict__ out, int H, float eps) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[32];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t r = blockIdx.x;
+  float* hr = h + r * H;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = hr[i];
+    if (n_partials > 0) {
+      constexpr int kInFlight = 8;
+      const float* p = partials + r * H + i;
+      float part[kInFlight];
+#pragma unroll
+      for (int s = 0; s < kInFlight; ++s)
+        if (s < n_partials) part[s] = p[s * partial_stride];
+      float ps = part[0];
+#pragma unroll
+      for (int s = 1; s < kInFlight; ++s)
+        if (s < n_partials) ps += part[s];
+      for (int s = kInFlight; s < n_partials; ++s) ps += p[s * partial_stride];
+      v += ps;
+      hr[i] = v;
+    }
+    row[i] = v;
+    sum += v;
+  }
+  const float mean = sb::block_sum(sum, red) / static_cast<float>(H);
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float d = row[i] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float scale = 1.0f / sqrtf(sb::block_sum(sq, red) / static_cast<float>(H) + eps);
+  TO* o = out + r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    o[i] = sb::narrow<TO>(fmaf((row[i] - mean) * scale, sb::widen(weight[i]), sb::widen(bias[i])));
+}
+
 }  // namespace
+
+// Layer norm with gain and bias over rows of H; arguments as sb_rmsnorm, plus the bias (of the gain's dtype).
+SB_EXPORT int sb_layernorm(float* h, const float* partials, int n_partials, int64_t partial_stride, const void* weight,
+                           const void* bias, int weight_dtype, void* out, int out_dtype, int n, int H, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const size_t smem = static_cast<size_t>(H) * sizeof(float);
+  if (smem > 200 * 1024) return sb::fail("sb_layernorm: width %d does not fit the row buffer (max 51200)", H);
+  const int threads = H >= 4096 ? 1024 : H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+#define SB_LN(TW, TO)                                                                                                       \
+  do {                                                                                                                      \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    sb::launch_pdl(layernorm_kernel<TW, TO>, n, threads, smem, stream, h, partials, n_partials, partial_stride,             \
+                   static_cast<const TW*>(weight), static_cast<const TW*>(bias), static_cast<TO*>(out), H, eps);            \
+  } while (0)
+  if (weight_dtype == 0 && out_dtype == 0) SB_LN(float, float);
+  else if (weight_dtype == 0 && out_dtype == 1) SB_LN(float, bf16);
+  else if (weight_dtype == 1 && out_dtype == 0) SB_LN(bf16, float);
+  else if (weight_dtype == 1 && out_dtype == 1) SB_LN(bf16, bf16);
+  else return sb::fail("sb_layernorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
+#undef SB_LN
+  return sb::check_launch("sb_layernorm");
+}
 
 // dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
 SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_t partial_stride, const void* weight,
@@ -266,4 +335,16 @@ SB_EXPORT int sb_op_rmsnorm(const SbOp* op, const SbStep* s, void* stream) {
   const int P = partials ? partial_count(op->i[2], op->i[3], n) : 0;
   return sb_rmsnorm(ptr<float>(op->i[0]), partials, P, static_cast<int64_t>(n) * op->i[8], ptr<const void>(op->i[4]), (int)op->i[5],
                     ptr<void>(op->i[6]), (int)op->i[7], n, (int)op->i[8], static_cast<float>(op->f[0]), static_cast<cudaStream_t>(stream));
+}
+
+// i: as sb_op_rmsnorm, and 10 the bias
+SB_EXPORT int sb_op_layernorm(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const int n = op->i[9] ? s->wanted : s->n;
+  if (n <= 0) return SB_OP_SKIPPED;
+  const float* partials = ptr<const float>(op->i[1]);
+  const int P = partials ? partial_count(op->i[2], op->i[3], n) : 0;
+  return sb_layernorm(ptr<float>(op->i[0]), partials, P, static_cast<int64_t>(n) * op->i[8], ptr<const void>(op->i[4]), ptr<const void>(op->i[10]),
+                      (int)op->i[5], ptr<void>(op->i[6]), (int)op->i[7], n, (int)op->i[8], static_cast<float>(op->f[0]),
+                      static_cast<cudaStream_t>(stream));
 }

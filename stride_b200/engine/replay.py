@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page (default 64)")
-    ap.add_argument("--max-requests", type=int, default=16, help="most requests alive at once")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests alive at once (state slots)")
     ap.add_argument("--kv-shuffle", type=int, default=0, help="hand out pages in a random order (seed; 0 = off)")
     ap.add_argument("--device", default="cuda:0")
     a = ap.parse_args(argv)

@@ -91,7 +91,7 @@ class Linear:
     def _tc_op(self, program, x, out, mode: int, splits: int = 1, wanted_rows: bool = False) -> None:
         # the decode chain has phases for partial sums per K range and for SwiGLU, on the step's tokens
         phase = None
-        if not wanted_rows and mode in (1, 3):
+        if not wanted_rows and mode in (1, 3):      # (the chain's gated epilogue is silu's: mode 4 has no phase)
             phase = lambda chain: chain.linear(x, self.weight, out, mode == 3, splits if mode == 1 else 1)
         program.add("gemm_tc", "sb_op_linear_tc", [x, x.stride(0), self.weight, self.weight.stride(0), out, self.out_features,
                                                     self.in_features, mode, splits, int(wanted_rows)], chain=phase)
@@ -125,22 +125,23 @@ class Linear:
         else:
             self._f32_op(program, x, program.h, program.h.stride(0), True, False)
 
-    def emit_swiglu(self, program, x: torch.Tensor, z: torch.Tensor, scratch_fn) -> None:
+    def emit_swiglu(self, program, x: torch.Tensor, z: torch.Tensor, scratch_fn, activation: str = "silu") -> None:
         """`forward_swiglu`."""
+        act = ops.GATE_ACTIVATIONS[activation]
         if self._tc(x) and z.dtype == torch.bfloat16:
-            self._tc_op(program, x, z, 3)
+            self._tc_op(program, x, z, 3 + act)
         else:
             gate_up = scratch_fn()
             self._f32_op(program, x, gate_up, gate_up.stride(0), False, False)
-            program.add("elementwise", "sb_op_swiglu", [gate_up, z, z.dtype, self.out_features // 2])
+            program.add("elementwise", "sb_op_swiglu", [gate_up, z, z.dtype, self.out_features // 2, act])
 
-    def forward_swiglu(self, x: torch.Tensor, z: torch.Tensor, scratch_fn) -> None:
-        """W = [gate rows; up rows]: z[n, I] = silu(x . gate^T) * (x . up^T). `scratch_fn()` gives a
-        float32 [n, 2 I] buffer for the unfused path."""
+    def forward_swiglu(self, x: torch.Tensor, z: torch.Tensor, scratch_fn, activation: str = "silu") -> None:
+        """W = [gate rows; up rows]: z[n, I] = act(x . gate^T) * (x . up^T), act = silu or the tanh form of gelu.
+        `scratch_fn()` gives a float32 [n, 2 I] buffer for the unfused path."""
         I = self.out_features // 2
         if self._tc(x) and z.dtype == torch.bfloat16:
-            ops.gemm_tc(x, self.weight, z, ops.SWIGLU, half_rows=I)
+            ops.gemm_tc(x, self.weight, z, ops.SWIGLU + ops.GATE_ACTIVATIONS[activation], half_rows=I)
         else:
             gate_up = scratch_fn()
             ops.gemm_f32(x, self.weight, gate_up, accumulate=False)
-            ops.swiglu(gate_up, z)
+            ops.swiglu(gate_up, z, activation)

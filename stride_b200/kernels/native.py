@@ -148,6 +148,7 @@ class StepProgram:
         self.max_rows = max_rows
         self.few_tokens = few_tokens          # up to this many tokens a projection leaves one buffer per K range
         self.h = None                         # the residual stream [max_rows, hidden] float32
+        self.embedding_output = None          # the embedding's rows [max_rows, hidden] float32, when a part reads them again
         self.pending = None                   # (flat buffer, K ranges, width) left by the last projection, or None
         self._libraries: list = []            # per operation: the library its function lives in (for its error text)
         self._keep: list = []                 # tensors the operations point into

@@ -66,13 +66,65 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, slots=None, sampled=None) -> None:
-    """out[i, :] = float32(table[tokens[i], :]); a token of -1 means sampled[slots[i]] (the request's last sampled token)."""
-    _cuda(tokens, table, out, slots, sampled)
-    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, slots=None, sampled=None, copy=None) -> None:
+    """out[i, :] = float32(table[tokens[i], :]); a token of -1 means sampled[slots[i]] (the request's last sampled token).
+    `copy` (float32, the shape of out) receives the same rows."""
+    _cuda(tokens, table, out, slots, sampled, copy)
+    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     n, H = out.shape
     _check(lib, fn(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out), n, H, table.shape[0], _ptr(slots),
-                   _ptr(sampled) if slots is not None else 0, _stream()))
+                   _ptr(sampled) if slots is not None else 0, _ptr(copy), _stream()))
+
+
+def layernorm(h: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor, partials=None) -> None:
+    """out = (x - mean(x)) / sqrt(var(x) + eps) * weight + bias with x = h (+ partials[0] + partials[1] ...), folded into h
+    in place as `rmsnorm` does."""
+    _cuda(h, weight, bias, out, partials)
+    if weight.dtype != bias.dtype:
+        raise TypeError("layernorm takes a gain and a bias of one dtype")
+    lib, fn = _fn("norm", "sb_layernorm", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                           c_int, c_int, c_float, c_void_p])
+    n, H = h.shape
+    S = 0 if partials is None else partials.shape[0]
+    stride = 0 if partials is None else partials.stride(0)
+    _check(lib, fn(_ptr(h), _ptr(partials), S, stride, _ptr(weight), _ptr(bias), dtype_code(weight.dtype), _ptr(out),
+                   dtype_code(out.dtype), n, H, eps, _stream()))
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, partials=None) -> None:
+    """out[i] = [a[i] (+ partials[s, i] for every s, ascending); b[i]]: float32 [n, H] twice into [n, 2 H] of out's dtype."""
+    _cuda(a, b, out, partials)
+    lib, fn = _fn("elementwise", "sb_concat_rows", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    n, H = a.shape
+    S = 0 if partials is None else partials.shape[0]
+    stride = 0 if partials is None else partials.stride(0)
+    _check(lib, fn(_ptr(a), _ptr(partials), S, stride, _ptr(b), _ptr(out), dtype_code(out.dtype), n, H, _stream()))
+
+
+def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, entry_meta: torch.Tensor, entries: int, decay: torch.Tensor,
+                   state: torch.Tensor, out: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> None:
+    """The decayed linear-attention recurrence for every entry of a step (csrc/lightning.cu). proj [S, n, width] float32:
+    partial sums of the projection with q, k, v at the given columns; entry_meta [4, E] on the device; state
+    [slots, heads, key_dim, value_dim] float32 (read unless the entry starts at position 0, written back); out [n, heads * value_dim]."""
+    _cuda(proj, entry_meta, decay, state, out)
+    lib, fn = _fn("lightning", "sb_lightning_scan", [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    if proj.dim() == 2:
+        proj = proj.unsqueeze(0)
+    _check(lib, fn(_ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], q_off, k_off, v_off, _ptr(entry_meta), entry_meta.stride(0),
+                   entries, _ptr(decay), _ptr(state), _ptr(out), heads, key_dim, value_dim, _stream()))
+
+
+def gated_rmsnorm(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * gain * sigmoid(gate), the gate being columns g_off.. of proj [S, n, width] (partial sums)."""
+    _cuda(o, proj, gain, out)
+    lib, fn = _fn("lightning", "sb_gated_rmsnorm", [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                                   c_int, c_int, c_float, c_void_p])
+    if proj.dim() == 2:
+        proj = proj.unsqueeze(0)
+    n, W = o.shape
+    _check(lib, fn(_ptr(o), _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], g_off, _ptr(gain), dtype_code(gain.dtype), _ptr(out),
+                   dtype_code(out.dtype), n, W, eps, _stream()))
 
 
 def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, partials=None) -> None:
@@ -91,30 +143,34 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 
 def rope_append(qkv: torch.Tensor, positions, slots, cos_sin, rotary_dim: int, q_out, cache_layer, block_table,
-                num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True) -> None:
+                num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True, values_from_keys: bool = False) -> None:
     """Rotate q and k of `qkv` [S, n, (Hq + 2 Hkv) D] (partials summed), store q, append k and v to the pages.
+    With `values_from_keys` qkv is [S, n, (Hq + Hkv) D] and a value head is its key head before rotation.
 
     `cache_layer` is this layer's view [pages, 2, Hkv, page_size, D] of the arena.
     """
     _cuda(qkv, positions, slots, cos_sin, q_out, cache_layer, block_table)
     lib, fn = _fn("elementwise", "sb_rope_append",
                   [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
-                   c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                   c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     if qkv.dim() == 2:
         qkv = qkv.unsqueeze(0)
     S, n, _ = qkv.shape
     _check(lib, fn(_ptr(qkv), S, qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_sin), rotary_dim, _ptr(q_out),
                    dtype_code(q_out.dtype), _ptr(cache_layer), dtype_code(cache_layer.dtype), _ptr(block_table),
                    block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0), cache_layer.stride(1),
-                   cache_layer.stride(2), n, num_heads, num_kv_heads, head_dim, int(write_kv), _stream()))
+                   cache_layer.stride(2), n, num_heads, num_kv_heads, head_dim, int(write_kv), int(values_from_keys), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[n, I] = act(gate_up[:, :I]) * gate_up[:, I:], act = silu or the tanh form of gelu."""
     _cuda(gate_up, out)
-    lib, fn = _fn("elementwise", "sb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    lib, fn = _fn("elementwise", "sb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     n, I = out.shape
-    _check(lib, fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, I, _stream()))
+    _check(lib, fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, I, GATE_ACTIVATIONS[activation], _stream()))
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor, partials=None) -> None:
@@ -175,7 +231,7 @@ def sample_temperature(logits, temperatures, seeds, lengths, tokens, values, sca
                    _ptr(scatter) if scatter_index is not None else 0, _stream()))
 
 
-STORE, ADD, SWIGLU = 0, 1, 2
+STORE, ADD, SWIGLU, GEGLU_TANH = 0, 1, 2, 3     # GEGLU_TANH: SWIGLU with the tanh form of gelu on the gate
 
 
 def gemm_tc_splits(M: int, K: int) -> int:
@@ -206,7 +262,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     _cuda(x, weight, out)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise TypeError("gemm_tc takes bfloat16 operands")
-    want = torch.bfloat16 if epilogue == SWIGLU else torch.float32
+    want = torch.bfloat16 if epilogue in (SWIGLU, GEGLU_TANH) else torch.float32
     if out.dtype != want:
         raise TypeError(f"gemm_tc epilogue {epilogue} writes {want}")
     lib, fn = _fn("gemm_tc", "sb_gemm_tc", [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,

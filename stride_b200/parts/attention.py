@@ -26,8 +26,9 @@ from .spec import TensorPlan
 @register_part("mixer", "attention")
 class AttentionMixer(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all keys),
-    position (a PartSpec of category "position", or None), scale (default head_dim ** -0.5).
-    tensors: q, k, v, o."""
+    position (a PartSpec of category "position", or None), scale (default head_dim ** -0.5),
+    values_from_keys (True: there is no value projection; a token's values are its keys as projected, before rotation).
+    tensors: q, k, v (unless values_from_keys), o."""
     graph_safe = True
 
 
@@ -45,28 +46,30 @@ class AttentionMixer(Mixer):
         self.scale = float(np.float32(math.pow(float(self.head_dim), -0.5))) if scale is None else float(scale)
         pos = p.get("position")
         self.position = part_class("position", pos.kind)(pos, env) if pos is not None else None
+        self.values_from_keys = bool(p.get("values_from_keys", False))
         self.qkv = self.o = None
 
     @property
     def qkv_width(self):
-        return (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        return (self.num_heads + (1 if self.values_from_keys else 2) * self.num_kv_heads) * self.head_dim
 
     def tensor_plan(self):
         t, D = self.spec.tensors, self.head_dim
         plan = {t["q"]: TensorPlan((self.num_heads * D, self.hidden)),
                 t["k"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
-                t["v"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
                 t["o"]: TensorPlan((self.hidden, self.num_heads * D))}
+        if not self.values_from_keys:
+            plan[t["v"]] = TensorPlan((self.num_kv_heads * D, self.hidden))
         if self.position is not None:
             plan.update(self.position.tensor_plan())      # a position part may have tensors of its own (a learned table)
         return plan
 
     def bind(self, tensors):
         t = self.spec.tensors
-        q, k, v = tensors[t["q"]], tensors[t["k"]], tensors[t["v"]]
-        if not (q.dtype == k.dtype == v.dtype):
-            q, k, v = (w.to(torch.float32) for w in (q, k, v))
-        self.qkv = Linear(torch.cat([q, k, v], dim=0), self.env.compute_dtype)
+        ws = [tensors[t[r]] for r in (("q", "k") if self.values_from_keys else ("q", "k", "v"))]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.to(torch.float32) for w in ws]
+        self.qkv = Linear(torch.cat(ws, dim=0), self.env.compute_dtype)
         self.o = Linear(tensors[t["o"]], self.env.compute_dtype)
         if self.position is None:
             # No rotation: a table of cos = 1, sin = 0 is never read because rotary_dim is 0.
@@ -134,7 +137,7 @@ class AttentionMixer(Mixer):
         if tensor_core:
             tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
             plan = self._tc_plan(ctx, G, 128 if tc5 else 64)
-        if (plan is not None and plan[1] == 0 and cache.writes and self._rotary == D
+        if (plan is not None and plan[1] == 0 and cache.writes and self._rotary == D and not self.values_from_keys
                 and plan[2] * self.num_kv_heads * plan[3] <= ops.attention_decode_rope_limit()):
             # only decoded tokens and very short portions, few enough for all CTAs to run at once: rotation and append
             # happen inside the decode kernel (the same bits; with more CTAs than that the separate kernel is faster)
@@ -147,7 +150,7 @@ class AttentionMixer(Mixer):
             return
         q = ws.get("attn.q", n, (self.num_heads * D,), ctx.act_dtype)
         ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
-                        self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
+                        self.num_heads, self.num_kv_heads, D, write_kv=cache.writes, values_from_keys=self.values_from_keys)
         if tensor_core:
             # prompt portions: the tcgen05 kernel where the page size allows it (tiles of 128 rows), else mma.sync (64 rows);
             # decoded tokens and very short portions: the split-key decode kernel
@@ -183,14 +186,15 @@ class AttentionMixer(Mixer):
         plan = -1
         if tensor_core:
             tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
-            fused = cache.writes and self._rotary == D
+            fused = cache.writes and self._rotary == D and not self.values_from_keys
             plan = program.plan(G, 128 if tc5 else 64, self.num_kv_heads, ops.attention_decode_rope_limit() if fused else -1)
         # (in a step of decoded tokens only, rotation and append can happen inside the attention kernel: the decode chain
         # counts on it, so it takes this mixer only with a fully rotated head and a cache of its own)
         program.add("elementwise", "sb_op_rope_append",
                     [qkv, self.qkv_width, S, program.few_tokens, self._cos_sin, self._rotary, q, q.dtype, pages, pages.dtype, table,
                      table.shape[1], pages.shape[3], pages.stride(0), pages.stride(1), pages.stride(2), self.num_heads,
-                     self.num_kv_heads, D, int(cache.writes), plan], chain=NO_PHASE if tensor_core and fused else None)
+                     self.num_kv_heads, D, int(cache.writes), plan, int(self.values_from_keys)],
+                    chain=NO_PHASE if tensor_core and fused else None)
         if tensor_core:
             if tc5:
                 program.add("attention_tc5", "sb_op_attention_tc5",

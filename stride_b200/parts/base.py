@@ -1,8 +1,8 @@
 """Interfaces of the parts a model is put together from, and the part registry.
 
 A part knows its own sizes and constants (from its `PartSpec`) and nothing about
-the model it sits in. Five categories exist: "norm", "position", "mixer",
-"feed_forward" and "block" (plus "embedding" and "head" at the ends of the model).
+the model it sits in. Six categories exist: "norm", "position", "mixer",
+"feed_forward", "rewrite" and "block" (plus "embedding" and "head" at the ends of the model).
 A new kind is one class registered under a category:
 
     @register_part("mixer", "my_kind")
@@ -29,7 +29,7 @@ from .spec import PartSpec, TensorPlan
 
 _REGISTRY: dict = {}
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "rewrite", "block", "embedding", "head")
 
 
 def register_part(category: str, kind: str):
@@ -158,6 +158,16 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Rewrite(Part):
+    """A part that replaces the residual stream by a function of it (and, if it sets `reads_embedding`, of the embedding
+    output, which the model then keeps for the whole step): what stands between two passes over a group of layers."""
+    reads_embedding = False
+
+    def forward(self, ctx, stream) -> None:
+        """stream.h <- f(stream.h [+ pending partial sums], ctx.embedding_output)."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """An arrangement of parts around the residual stream. `ROLES` names the parts a block of this kind is made of
     and the registry category of each; the model builds them from the layer's `LayerSpec.parts` and hands them over
@@ -181,6 +191,11 @@ class Block(Part):
 
     def all_parts(self):
         return tuple(self.parts[r] for r in self.ROLES)
+
+    @property
+    def reads_embedding(self) -> bool:
+        """True if a part of this block reads the embedding output again (the model then keeps a copy of it)."""
+        return any(getattr(p, "reads_embedding", False) for p in self.all_parts())
 
     def cache_need(self):
         """What this block's layer asks of the cache manager: by default what its part in the role "mixer" asks."""

@@ -110,6 +110,7 @@ class StepContext:
     upload_ints: Optional[object] = None                   # callable(np.ndarray int32) -> device tensor, valid for this step
     sampled: Optional[torch.Tensor] = None                 # [slots] int32: each request's last sampled token (a token id of -1 reads it)
     shared: dict = field(default_factory=dict)             # what parts compute once per step and share between layers
+    embedding_output: Optional[torch.Tensor] = None        # [n, hidden] float32: the embedding's rows, kept when a part reads them again
     # Set for a step that is recorded into a CUDA graph: every entry is one decoded token, the batch is
     # padded to a fixed size, and no key lies at or beyond `static_keys`. Parts must then launch the same
     # kernels with the same arguments whatever the positions are, and must not copy from the host.

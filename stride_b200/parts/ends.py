@@ -35,11 +35,12 @@ class Embedding(Part):
     def weight_bytes(self):
         return 0   # a step reads one row per token, not the table
 
-    def forward(self, ctx, out):
-        ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled)
+    def forward(self, ctx, out, copy=None):
+        """`copy`: a second buffer for the same rows, for models whose later layers read the embedding again."""
+        ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled, copy)
 
-    def emit(self, program, out, sampled):
-        program.add("elementwise", "sb_op_embed", [self.weight, self.weight.dtype, out, self.hidden, self.weight.shape[0], sampled])
+    def emit(self, program, out, sampled, copy=None):
+        program.add("elementwise", "sb_op_embed", [self.weight, self.weight.dtype, out, self.hidden, self.weight.shape[0], sampled, copy])
 
 
 @register_part("head", "linear")

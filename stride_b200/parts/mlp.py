@@ -1,6 +1,7 @@
-"""The gated feed-forward of Llama: h += W2 (silu(W1 x) * (W3 x)), silu(a) = a / (1 + exp(-a))
+"""The gated feed-forward: h += W2 (act(W1 x) * (W3 x)). Llama's has act = silu, silu(a) = a / (1 + exp(-a))
 (arhaamatiq/stride src/kernels.cu:329-363, src/numerics.h:33; down projection added to the
-residual: src/kernels.cu:294-325). gate_proj = W1, up_proj = W3, down_proj = W2."""
+residual: src/kernels.cu:294-325); gate_proj = W1, up_proj = W3, down_proj = W2. The parameter `activation`
+selects another gate: "gelu_tanh", 0.5 a (1 + tanh(sqrt(2/pi) (a + 0.044715 a^3)))."""
 from __future__ import annotations
 
 import torch
@@ -11,9 +12,10 @@ from .base import FeedForward, register_part
 from .spec import TensorPlan
 
 
+@register_part("feed_forward", "gated")
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size. tensors: gate, up, down."""
+    """params: hidden_size, intermediate_size, activation ("silu" by default, or "gelu_tanh"). tensors: gate, up, down."""
     graph_safe = True
 
 
@@ -21,6 +23,9 @@ class SwiGLU(FeedForward):
         super().__init__(spec, env)
         self.hidden = int(spec.params["hidden_size"])
         self.intermediate = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: unknown activation '{self.activation}' (known: {', '.join(ops.GATE_ACTIVATIONS)})")
         self.gate_up = self.down = None
 
     def tensor_plan(self):
@@ -46,11 +51,13 @@ class SwiGLU(FeedForward):
     def forward(self, ctx, x, stream):
         n, ws = ctx.n, ctx.workspace
         z = ws.get("mlp.z", n, (self.intermediate,), ctx.act_dtype)
-        self.gate_up.forward_swiglu(x, z, lambda: ws.get("mlp.gate_up", n, (2 * self.intermediate,), torch.float32))
+        self.gate_up.forward_swiglu(x, z, lambda: ws.get("mlp.gate_up", n, (2 * self.intermediate,), torch.float32),
+                                    self.activation)
         self.down.forward_add(z, stream, ws.raw("mlp.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))
 
     def emit(self, program, x):
         ws = program.workspace
         z = ws.get("mlp.z", ws.max_tokens, (self.intermediate,), self.env.act_dtype)
-        self.gate_up.emit_swiglu(program, x, z, lambda: ws.get("mlp.gate_up", ws.max_tokens, (2 * self.intermediate,), torch.float32))
+        self.gate_up.emit_swiglu(program, x, z, lambda: ws.get("mlp.gate_up", ws.max_tokens, (2 * self.intermediate,), torch.float32),
+                                 self.activation)
         self.down.emit_add(program, z, ws.raw("mlp.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))

@@ -31,6 +31,11 @@ class DecoderModel:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")
 
     @property
+    def keeps_embedding(self) -> bool:
+        """True if a scheduled layer reads the embedding output again: the embedding then writes its rows twice."""
+        return any(self.blocks[e.layer].reads_embedding for e in self.spec.schedule)
+
+    @property
     def graph_safe(self) -> bool:
         return (self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
                 and all(b.all_graph_safe for b in self.blocks))
@@ -80,7 +85,11 @@ class DecoderModel:
         rows listed in `logit_rows` (int32, device), or None when count is 0."""
         ws, H = ctx.workspace, self.spec.hidden_size
         stream = ResidualStream(ws.get("model.h", ctx.n, (H,), torch.float32))
-        self.embedding.forward(ctx, stream.h)
+        if self.keeps_embedding:
+            ctx.embedding_output = ws.get("model.embedding_output", ctx.n, (H,), torch.float32)
+            self.embedding.forward(ctx, stream.h, ctx.embedding_output)
+        else:
+            self.embedding.forward(ctx, stream.h)
         for i, e in enumerate(self.spec.schedule):
             self.blocks[e.layer].forward(ctx, stream, caches[i])
         if count == 0:
@@ -101,7 +110,11 @@ class DecoderModel:
         has no native form."""
         ws, H = program.workspace, self.spec.hidden_size
         program.h = ws.get("model.h", ws.max_tokens, (H,), torch.float32)
-        self.embedding.emit(program, program.h, sampled)
+        if self.keeps_embedding:
+            program.embedding_output = ws.get("model.embedding_output", ws.max_tokens, (H,), torch.float32)
+            self.embedding.emit(program, program.h, sampled, program.embedding_output)
+        else:
+            self.embedding.emit(program, program.h, sampled)
         chained = self.env.decode_chain and "decode_chain" in self.kernel_libraries()
         if chained:
             # every operation of the layers also names its phase of the decode chain; if all of them have one, one

@@ -49,3 +49,50 @@ class RMSNorm(Norm):
 
     def emit_rows(self, program, rows, out):
         self._op(program, rows, None, out, True)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w + b, var the mean squared deviation, all in 32-bit.
+    params: size, eps. tensors: weight, bias."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.weight = self.bias = None
+
+    def tensor_plan(self):
+        t = self.spec.tensors
+        return {t["weight"]: TensorPlan((self.size,)), t["bias"]: TensorPlan((self.size,), zero_mean=True)}
+
+    def bind(self, tensors):
+        t = self.spec.tensors
+        w, b = tensors[t["weight"]], tensors[t["bias"]]
+        if w.dtype != b.dtype:
+            w, b = w.float(), b.float()
+        self.weight, self.bias = w.contiguous(), b.contiguous()
+
+    def weight_bytes(self):
+        return 2 * self.weight.numel() * self.weight.element_size()
+
+    def kernel_libraries(self):
+        return {"norm"}
+
+    def forward(self, ctx, stream, out):
+        ops.layernorm(stream.h, self.weight, self.bias, self.eps, out, partials=stream.take_pending())
+
+    def forward_rows(self, rows, out):
+        ops.layernorm(rows, self.weight, self.bias, self.eps, out)
+
+    def _op(self, program, h, pending, out, wanted_rows: bool):
+        flat, S, _ = pending if pending is not None else (None, 1, 0)
+        program.add("norm", "sb_op_layernorm", [h, flat, S, program.few_tokens, self.weight, self.weight.dtype, out, out.dtype, self.size,
+                                                int(wanted_rows), self.bias], [self.eps])
+
+    def emit(self, program, out):
+        self._op(program, program.h, program.take_pending(), out, False)
+
+    def emit_rows(self, program, rows, out):
+        self._op(program, rows, None, out, True)

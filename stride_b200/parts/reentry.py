@@ -1,0 +1,52 @@
+"""Re-entry of the embedding into the residual stream: h <- W [h; e], e being the embedding output of the same
+token and W a [hidden, 2 hidden] matrix whose first half of columns meets h. Models that run a group of layers
+several times put it in front of every pass, so that each pass sees the token itself beside what the pass before made
+of it. The two streams are laid side by side in the activation dtype (the stream's pending partial sums folded in on the
+way) and go through one matrix product that overwrites h."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..kernels.linear import Linear
+from .base import Rewrite, register_part
+from .spec import TensorPlan
+
+
+@register_part("rewrite", "embedding_mix")
+class EmbeddingMix(Rewrite):
+    """params: hidden_size. tensors: weight [hidden, 2 hidden]."""
+    graph_safe = True
+    reads_embedding = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.params["hidden_size"])
+        self.linear = None
+
+    def tensor_plan(self):
+        return {self.spec.tensors["weight"]: TensorPlan((self.hidden, 2 * self.hidden))}
+
+    def bind(self, tensors):
+        self.linear = Linear(tensors[self.spec.tensors["weight"]], self.env.compute_dtype)
+
+    def weight_bytes(self):
+        return self.linear.weight_bytes()
+
+    def kernel_libraries(self):
+        return {"elementwise", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
+
+    def forward(self, ctx, stream):
+        if ctx.embedding_output is None:
+            raise RuntimeError("embedding_mix: the model did not keep the embedding output")
+        both = ctx.workspace.get("reentry.both", ctx.n, (2 * self.hidden,), ctx.act_dtype)
+        ops.concat_rows(stream.h, ctx.embedding_output, both, partials=stream.take_pending())
+        self.linear.forward(both, stream.h)
+
+    def emit(self, program):
+        ws = program.workspace
+        both = ws.get("reentry.both", ws.max_tokens, (2 * self.hidden,), self.env.act_dtype)
+        flat, S, _ = program.take_pending() or (None, 1, 0)
+        program.add("elementwise", "sb_op_concat_rows", [program.h, flat, S, program.few_tokens, program.embedding_output, both, both.dtype,
+                                                          self.hidden])
+        self.linear.emit(program, both, program.h)

@@ -99,3 +99,4 @@ class TensorPlan:
     shape: tuple
     optional: bool = False
     integer: bool = False
+    zero_mean: bool = False      # a vector that is added, not multiplied (a bias): random weights are N(0, .), not 1 + N(0, .)

@@ -2,7 +2,7 @@
 configuration and a seed, or the same tensors directly on a device.
 
 Matrices are N(0, std) with std 0.02, norm gains 1 + N(0, gain_std) (0.1 by default, so
-that a norm weight that is dropped or misplaced changes the result). Every tensor has its
+that a norm weight that is dropped or misplaced changes the result), biases N(0, gain_std). Every tensor has its
 own generator seeded from (seed, tensor name), so a tensor's values depend on neither
 the order of generation nor the other tensors. arhaamatiq/stride has no such mode in its
 engine; its tests build a tiny model with a Python script (tests/make_tiny_model.py:19-54).
@@ -47,6 +47,8 @@ def random_tensors(config: dict, seed: int, device="cpu", dtype=torch.bfloat16, 
         gen = torch.Generator(device=device).manual_seed(_tensor_seed(seed, name))
         if want.integer:
             out[name] = torch.zeros(want.shape, dtype=torch.int32, device=device)
+        elif len(want.shape) == 1 and want.zero_mean:
+            out[name] = (gain_std * torch.randn(want.shape, generator=gen, device=device, dtype=torch.float32)).to(dtype)
         elif len(want.shape) == 1:
             out[name] = (1.0 + gain_std * torch.randn(want.shape, generator=gen, device=device, dtype=torch.float32)).to(dtype)
         else:
