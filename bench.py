@@ -327,6 +327,150 @@ def reference_arm(a) -> int:
 
 
 # ---------------------------------------------------------------------------------------------------- this engine
+# ---------------------------------------------------------------------------------------------------- another design beside Llama
+def _keralorn_config(width: int, ff: int, vocab: int, pairs: int, window: int) -> dict:
+    """`pairs` times (windowed attention, lightning), each with a feed-forward, all inside one pass of the loop: the
+    attention layer has the heads of the Llama 3.2 1B layer, the lightning layer 16 heads of 128 x 128."""
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": window},
+                     "rot": {"dims": 32, "base": 500000.0, "scaling": {"factor": 32.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    heads = width // 128
+    lig = {"type": "lightning", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3 - 5.0 * h / max(heads - 1, 1)) for h in range(heads)]}}
+    return {"architecture": "Keralorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": [att, lig] * pairs,
+            "loop": {"start": 0, "stop": 2 * pairs, "times": 1}}
+
+
+def design_compare(a) -> int:
+    """Keralorn at layer sizes of a real model beside LlamaForCausalLM with as many layers of the same width, heads and
+    feed-forward (random weights, bfloat16 engine): a prompt of 2,048 tokens in one step, decode steps at batch 8 and 64
+    from CUDA graphs; then Keralorn's own kernels alone against their rooflines. One JSON line."""
+    import torch
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.kernels import ops
+
+    pk = peaks()
+    width, ff, vocab, pairs, page, context = 2048, 8192, 32000, 2, 64, 4096
+    layers = 2 * pairs
+    llama = _llama(width, ff, layers, width // 64, width // 256, 64, False, 32.0, context)
+    llama["vocab_size"] = vocab
+    configs = {"keralorn": _keralorn_config(width, ff, vocab, pairs, 1024), "llama": llama}
+    gen = torch.Generator().manual_seed(3)
+    out = {"design": "keralorn", "beside": "LlamaForCausalLM", "width": width, "ff": ff, "layers": layers, "vocab": vocab,
+           "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": pk,
+           "l2": "weights and caches of a step exceed the 126 MB L2; the kernel timings flush L2 between launches"}
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps, prepare=None, clear=False):
+        ts = []
+        for r in range(reps + 3):
+            if prepare:
+                prepare()
+            if clear:
+                flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if r >= 3:
+                ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    clocks = ClockSampler()
+    clocks.start()
+    for name, cfg in configs.items():
+        opts = EngineOptions(dtype="bfloat16", max_rows=PREFILL_TOKENS, max_full_rows=64, max_slots=65,
+                             kv_pages=64 * 12 + PREFILL_TOKENS // page + 8, page_size=page, max_context=context)
+        eng = Engine.from_random(cfg, seed=0, options=opts)
+        cache = eng.cache
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        held = {}
+
+        def prefill_prepare():
+            if "slot" in held:
+                cache.release_slot(held["slot"])
+            held["slot"] = cache.acquire_slot()
+            cache.ensure(held["slot"], PREFILL_TOKENS)
+
+        ms = timed(lambda: eng.step([StepEntry(held["slot"], 0, toks, [PREFILL_TOKENS - 1])]), 5, prefill_prepare)
+        cache.release_slot(held.pop("slot"))
+        res = {"prefill_2048_ms": round(ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / ms * 1e3), "weight_bytes_per_step": eng.weight_bytes_per_step(),
+               "native_step": eng._program is not None}
+        for batch in (8, 64):
+            slots = [cache.acquire_slot() for _ in range(batch)]
+            prompt = torch.randint(0, vocab, (batch, 512), generator=gen).tolist()
+            for b, s_ in enumerate(slots):
+                cache.ensure(s_, 512)
+                eng.step([StepEntry(s_, 0, prompt[b], [])])
+            pos = [512]
+
+            def one():
+                entries = []
+                for b, s_ in enumerate(slots):
+                    cache.ensure(s_, pos[0] + 1)
+                    entries.append(StepEntry(s_, pos[0], [prompt[b][pos[0] % 512]], [0]))
+                eng.step(entries)
+                pos[0] += 1
+
+            for _ in range(a.warmup):
+                one()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            steps = min(a.steps, 128)
+            e0.record()
+            for _ in range(steps):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            res[f"decode_b{batch}_ms"] = round(ms, 4)
+            res[f"decode_b{batch}_tok_s"] = round(batch / ms * 1e3)
+            res[f"decode_b{batch}_hbm_fraction_of_measured"] = round(eng.weight_bytes_per_step() / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)
+            for s_ in slots:
+                cache.release_slot(s_)
+        out[name] = res
+        del eng
+        torch.cuda.empty_cache()
+
+    # Keralorn's own kernels alone, beside the like kernel of Llama where there is one
+    H, D, V = width // 128, 128, 128
+    kern = {}
+    dev = "cuda"
+    decay = torch.full((H,), 0.99, device=dev)
+    for label, entries, length in (("scan_prefill_2048", 1, 2048), ("scan_prefill_8x2048", 8, 2048), ("scan_decode_b64", 64, 1), ("scan_decode_b512", 512, 1)):
+        n = entries * length
+        proj = torch.randn(1, n, 2 * H * D + 2 * H * V, device=dev)
+        state = torch.zeros(entries + 1, H, D, V, device=dev)
+        o = torch.empty(n, H * V, device=dev)
+        meta = torch.tensor([list(range(entries)), [e * length for e in range(entries)], [length] * entries, [0 if length > 1 else 7] * entries],
+                            dtype=torch.int32, device=dev)
+        act = torch.empty(n * (2 * H * D + H * V), device=dev)
+        ms = timed(lambda: ops.lightning_scan(proj, 0, H * D, 2 * H * D, meta, entries, decay, state, o, H, D, V, act), 5, clear=True)
+        flops = 5.0 * n * H * D * V                      # per state element and token: a product, two fused multiply-adds
+        moved = 4.0 * (n * (2 * H * D + H * V) + n * H * V + (2 if length == 1 else 1) * entries * H * D * V)
+        kern[label] = {"ms": round(ms, 4), "tflops_fp32": round(flops / ms / 1e9, 2), "gb_s": round(moved / ms / 1e6, 1),
+                       "hbm_fraction_of_measured": round(moved / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)}
+    for n in (64, 2048):
+        proj = torch.randn(1, n, 2 * H * D + 2 * H * V, device=dev)
+        o = torch.randn(n, H * V, device=dev)
+        y = torch.empty(n, H * V, dtype=torch.bfloat16, device=dev)
+        gain = torch.ones(H * V, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.gated_rmsnorm(o, proj, 2 * H * D + H * V, gain, 1e-5, y), 5, clear=True)
+        kern[f"gated_rmsnorm_{n}"] = {"ms": round(ms, 4), "gb_s": round(n * H * V * 10.0 / ms / 1e6, 1)}
+        h = torch.randn(n, width, device=dev)
+        x = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+        g, b = torch.ones(width, dtype=torch.bfloat16, device=dev), torch.zeros(width, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.layernorm(h, g, b, 1e-5, x), 5, clear=True)
+        ms_r = timed(lambda: ops.rmsnorm(h, g, 1e-5, x), 5, clear=True)
+        kern[f"layernorm_{n}"] = {"ms": round(ms, 4), "gb_s": round(n * width * 6.0 / ms / 1e6, 1), "rmsnorm_ms": round(ms_r, 4)}
+    out["kernels"] = kern
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -337,9 +481,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="1b: the decode step (default); 3b, 8b: serving runs")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64, float32 and prefill measurements")
+    ap.add_argument("--design", default="", choices=["", "keralorn"],
+                    help="keralorn: prefill and decode of that design beside a Llama of equal layer sizes, and its own kernels alone")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design:
+        return design_compare(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2

@@ -276,10 +276,11 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __
 
 // ------------------------------------------------------------------ two streams side by side
 // out[r] = [a[r] (+ partial sums, ascending); b[r]] as one row of 2 H elements: the input of a projection that reads the
-// residual stream and a second stream of the same width together.
+// residual stream and a second stream of the same width together. clear_a: a is set to zero behind the read, for a
+// projection whose result replaces the stream and arrives as partial sums to be added to it.
 template <class TO>
-__global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ partials, int n_partials,
-                                   int64_t partial_stride, const float* __restrict__ b, TO* __restrict__ out, int H) {
+__global__ void concat_rows_kernel(float* __restrict__ a, const float* __restrict__ partials, int n_partials,
+                                   int64_t partial_stride, const float* __restrict__ b, TO* __restrict__ out, int H, int clear_a) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int64_t r = blockIdx.x;
@@ -293,6 +294,7 @@ __global__ void concat_rows_kernel(const float* __restrict__ a, const float* __r
     }
     out[r * 2 * H + i] = sb::narrow<TO>(v);
     out[r * 2 * H + H + i] = sb::narrow<TO>(b[r * H + i]);
+    if (clear_a) a[r * H + i] = 0.0f;
   }
 }
 
@@ -300,13 +302,13 @@ __global__ void concat_rows_kernel(const float* __restrict__ a, const float* __r
 
 // dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
 
-SB_EXPORT int sb_concat_rows(const float* a, const float* partials, int n_partials, int64_t partial_stride, const float* b,
-                             void* out, int out_dtype, int n, int H, cudaStream_t stream) {
+SB_EXPORT int sb_concat_rows(float* a, const float* partials, int n_partials, int64_t partial_stride, const float* b,
+                             void* out, int out_dtype, int n, int H, int clear_a, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (out_dtype == 0)
-    sb::launch_pdl(concat_rows_kernel<float>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<float*>(out), H);
+    sb::launch_pdl(concat_rows_kernel<float>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<float*>(out), H, clear_a);
   else if (out_dtype == 1)
-    sb::launch_pdl(concat_rows_kernel<bf16>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<bf16*>(out), H);
+    sb::launch_pdl(concat_rows_kernel<bf16>, n, 256, 0, stream, a, partials, n_partials, partial_stride, b, static_cast<bf16*>(out), H, clear_a);
   else
     return sb::fail("sb_concat_rows: unsupported out dtype %d", out_dtype);
   return sb::check_launch("sb_concat_rows");
@@ -416,11 +418,11 @@ SB_EXPORT int sb_op_gather_rows(const SbOp* op, const SbStep* s, void* stream) {
 }
 
 // i: 0 a (float32 [n, H]), 1 pending partial sums on a (flat; 0: none), 2 K ranges S, 3 most tokens with a buffer per range,
-//    4 b (float32 [n, H]), 5 out [n, 2 H], 6 out dtype, 7 H
+//    4 b (float32 [n, H]), 5 out [n, 2 H], 6 out dtype, 7 H, 8 set a to zero behind the read
 SB_EXPORT int sb_op_concat_rows(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   const float* partials = ptr<const float>(op->i[1]);
   const int P = partials ? partial_count(op->i[2], op->i[3], s->n) : 0;
-  return sb_concat_rows(ptr<const float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[7], ptr<const float>(op->i[4]),
-                        ptr<void>(op->i[5]), (int)op->i[6], s->n, (int)op->i[7], static_cast<cudaStream_t>(stream));
+  return sb_concat_rows(ptr<float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[7], ptr<const float>(op->i[4]),
+                        ptr<void>(op->i[5]), (int)op->i[6], s->n, (int)op->i[7], (int)op->i[8], static_cast<cudaStream_t>(stream));
 }

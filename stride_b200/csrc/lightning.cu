@@ -8,8 +8,8 @@
 // range of value columns) and walks the request's tokens of this step in order, the state in registers; it reads
 // the state the step before left (or starts from zero at position 0) and writes it back at the end. A column of
 // the state depends on no other column, so the value columns may be spread over CTAs and warps in any way; the
-// D sums of an output are cut into parts of R consecutive elements, each one chain of fused multiply-adds in
-// ascending order, and the parts are added in ascending order. Neither depends on the step, so a token's output
+// D sums of an output are cut into parts of 16 consecutive elements, each two chains of fused multiply-adds (even and
+// odd elements, ascending, then added), and the parts are added in ascending order. Neither depends on the step, so a token's output
 // has the same bits however the sequence was cut into steps and whatever else the batch holds.
 //
 // The second kernel is what follows the recurrence: an RMS norm over all heads' outputs of a token, times a gain,
@@ -41,6 +41,8 @@ struct ScanParams {
   float* out;               // [n][H V]
   int H, D, V;
   int vc;                   // value columns a CTA owns (a multiple of 32)
+  int chunk;                // tokens staged in shared memory at a time (at most kChunk)
+  int activated;            // 1: proj already holds silu of the folded sums (lightning_activate_kernel ran)
 };
 
 // Sum of the projection's partial buffers at one element, ascending.
@@ -57,89 +59,273 @@ __device__ __forceinline__ float folded(const float* p, int n_partials, int64_t 
   return sum;
 }
 
-// blockDim.x = parts * vc: thread = (part of the D sums, value column). R elements of a state column per thread.
-template <int R>
-__global__ void __launch_bounds__(512) lightning_scan_kernel(const ScanParams p) {
+// 4-byte and 16-byte asynchronous copies from global to shared memory, and the wait for all of a thread's copies.
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int R = 16;   // elements of a state column a thread holds: a part of the D sums
+
+// Two float32 fused multiply-adds in one instruction (sm_100: fma.rn.f32x2): each half rounds as a scalar fma.rn does.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<const uint64_t*>(&a)), "l"(*reinterpret_cast<const uint64_t*>(&b)), "l"(*reinterpret_cast<const uint64_t*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+
+// A token's R keys and R queries of one part, as read from shared memory.
+struct TokenKQ {
+  float4 k[R / 4], q[R / 4];
+  __device__ __forceinline__ void load(const float4* k4, const float4* q4) {
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i) {
+      k[i] = k4[i];
+      q[i] = q4[i];
+    }
+  }
+};
+
+// One token of the recurrence for one thread: its R elements of a state column (as pairs), the token's R keys and queries
+// of this part and the column's value. S <- decay S + k v; returns the part's share of the output: the even and the odd
+// elements are a chain of fused multiply-adds each, ascending, and the two are added.
+__device__ __forceinline__ float scan_token(float2 (&S)[R / 2], const TokenKQ& x, float vv, float decay) {
+  const float2 v2 = make_float2(vv, vv), d2 = make_float2(decay, decay), zero = make_float2(0.0f, 0.0f);
+  float2 acc = zero;
+#pragma unroll
+  for (int i = 0; i < R / 4; ++i) {
+    S[2 * i] = fma2(d2, S[2 * i], fma2(make_float2(x.k[i].x, x.k[i].y), v2, zero));
+    acc = fma2(S[2 * i], make_float2(x.q[i].x, x.q[i].y), acc);
+    S[2 * i + 1] = fma2(d2, S[2 * i + 1], fma2(make_float2(x.k[i].z, x.k[i].w), v2, zero));
+    acc = fma2(S[2 * i + 1], make_float2(x.q[i].z, x.q[i].w), acc);
+  }
+  return acc.x + acc.y;
+}
+
+// Named barriers of lightning_scan_kernel (id 0 is __syncthreads): two of each kind, one per buffer.
+enum { kBarFull = 1, kBarEmpty = 4, kBarOutFull = 7, kBarOutEmpty = 9 };
+constexpr int kStages = 2;      // staging buffers of the recurrence's inputs (2 or 3): the loads run kStages - 1 chunks ahead
+template <int BASE>
+__device__ __forceinline__ void bar_sync(int b, int count) {
+  if (b == 0) asm volatile("bar.sync %0, %1;" ::"n"(BASE), "r"(count) : "memory");
+  else if (b == 1) asm volatile("bar.sync %0, %1;" ::"n"(BASE + 1), "r"(count) : "memory");
+  else asm volatile("bar.sync %0, %1;" ::"n"(BASE + 2), "r"(count) : "memory");
+}
+template <int BASE>
+__device__ __forceinline__ void bar_arrive(int b, int count) {
+  if (b == 0) asm volatile("bar.arrive %0, %1;" ::"n"(BASE), "r"(count) : "memory");
+  else if (b == 1) asm volatile("bar.arrive %0, %1;" ::"n"(BASE + 1), "r"(count) : "memory");
+  else asm volatile("bar.arrive %0, %1;" ::"n"(BASE + 2), "r"(count) : "memory");
+}
+
+// Prompt portions (and any step with an entry of more than one token). `proj` holds the activated sums (silu applied by
+// lightning_activate_kernel; one buffer). The CTA's first parts * vc threads compute: thread = (part of the D sums, value
+// column), a part's threads being whole warps, so that the keys and queries of a part are read from shared memory by
+// broadcast. Behind them one warp loads: it keeps the q, k, v rows of the next chunk of kChunk tokens on their way into
+// the other staging buffer (asynchronous copies); and vc / 32 warps store: they add the parts of the outputs of the chunk
+// before and write them to global memory, while the computing warps are already at the next chunk. The three groups meet
+// only at named barriers, one pair per buffer and direction.
+template <int VEC>
+__global__ void __launch_bounds__(576) lightning_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(16) float smem[];
   sb::grid_launch_dependents();
   const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * p.vc;
-  const int D = p.D, V = p.V, vc = p.vc;
-  const int parts = (D + R - 1) / R, Dp = parts * R;
-  const int part = threadIdx.x / vc, cl = threadIdx.x % vc, c = c0 + cl;
-  float* sq = smem;                      // [kChunk][Dp]
-  float* sk = sq + kChunk * Dp;          // [kChunk][Dp]
-  float* sv = sk + kChunk * Dp;          // [kChunk][vc]
-  float* so = sv + kChunk * vc;          // [parts][kChunk][vc]
+  const int vc = p.vc, parts = (p.D + R - 1) / R, Dp = parts * R;
+  const int vn = min(vc, p.V - c0);
+  const int NC = parts * vc, NS = vc;                  // computing threads, storing threads (one warp loads)
+  const int stage = kChunk * (2 * Dp + vc);            // floats of a staging buffer: q [kChunk][Dp], k [kChunk][Dp], v [kChunk][vc]
+  const int outs = parts * kChunk * vc;                // floats of an output buffer: [parts][kChunk][vc]
+  float* so = smem + kStages * stage;
   const int slot = p.meta[e], row0 = p.meta[p.meta_stride + e], len = p.meta[2 * p.meta_stride + e],
             pos0 = p.meta[3 * p.meta_stride + e];
-  const float decay = p.decay[h];
-  float S[R];
-  float* st = p.state + ((static_cast<int64_t>(slot) * p.H + h) * D + part * R) * V + c;
-  const bool live = c < V;
+  const int chunks = (len + kChunk - 1) / kChunk;
+  if (Dp != p.D || vn != vc) {
+    // nothing writes the cells beyond D and beyond the CTA's existing columns: they are zero for good
+    for (int b = 0; b < kStages; ++b)
+      for (int t = 0; t < kChunk; ++t) {
+        float* row = smem + b * stage;
+        for (int d = p.D + threadIdx.x; d < Dp; d += blockDim.x) row[t * Dp + d] = row[(kChunk + t) * Dp + d] = 0.0f;
+        for (int j = vn + threadIdx.x; j < vc; j += blockDim.x) row[2 * kChunk * Dp + t * vc + j] = 0.0f;
+      }
+  }
   sb::grid_dependency_wait();
+  __syncthreads();
+  const int tid = threadIdx.x;
+  if (tid < NC) {
+    // ---------------------------------------------------------------- the recurrence
+    const int part = tid / vc, cl = tid % vc;
+    const float decay = p.decay[h];
+    const bool live = cl < vn;
+    const int dn = min(R, p.D - part * R);            // elements of this part that exist
+    float* st = p.state + ((static_cast<int64_t>(slot) * p.H + h) * p.D + part * R) * p.V + c0 + cl;
+    float2 S[R / 2];
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = (pos0 > 0 && live && part * R + i < D) ? st[static_cast<int64_t>(i) * V] : 0.0f;
-
-  for (int t0 = 0; t0 < len; t0 += kChunk) {
-    const int nt = min(kChunk, len - t0);
-    __syncthreads();
-    // stage silu(q), silu(k) of this head and silu(v) of this CTA's columns for nt tokens
-    for (int idx = threadIdx.x; idx < nt * 2 * Dp; idx += blockDim.x) {
-      const int t = idx / (2 * Dp), j = idx % (2 * Dp);
-      const bool is_k = j >= Dp;
-      const int d = is_k ? j - Dp : j;
-      float v = 0.0f;
-      if (d < D) {
-        const float* src = p.proj + static_cast<int64_t>(row0 + t0 + t) * p.width + (is_k ? p.k_off : p.q_off) + h * D + d;
-        v = silu(folded(src, p.n_partials, p.partial_stride));
-      }
-      (is_k ? sk : sq)[t * Dp + d] = v;
+    for (int i = 0; i < R; ++i) {
+      const float v = (pos0 > 0 && live && i < dn) ? st[static_cast<int64_t>(i) * p.V] : 0.0f;
+      if (i & 1) S[i / 2].y = v;
+      else S[i / 2].x = v;
     }
-    for (int idx = threadIdx.x; idx < nt * vc; idx += blockDim.x) {
-      const int t = idx / vc, j = idx % vc;
-      float v = 0.0f;
-      if (c0 + j < V) {
-        const float* src = p.proj + static_cast<int64_t>(row0 + t0 + t) * p.width + p.v_off + h * V + c0 + j;
-        v = silu(folded(src, p.n_partials, p.partial_stride));
+    for (int c = 0, sb_ = 0; c < chunks; ++c, sb_ = sb_ + 1 == kStages ? 0 : sb_ + 1) {
+      const int b = c & 1, nt = min(kChunk, len - c * kChunk);
+      const float* sq = smem + sb_ * stage;
+      bar_sync<kBarFull>(sb_, NC + 32);
+      if (c >= 2) bar_sync<kBarOutEmpty>(b, NC + NS);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + part * R);
+      const float4* k4 = reinterpret_cast<const float4*>(sq + kChunk * Dp + part * R);
+      const float* sv = sq + 2 * kChunk * Dp + cl;
+      float* sop = so + b * outs + part * kChunk * vc + cl;
+#pragma unroll 2
+      for (int t = 0; t < nt; ++t) {
+        TokenKQ x;
+        x.load(k4, q4);
+        *sop = scan_token(S, x, *sv, decay);
+        k4 += Dp / 4;
+        q4 += Dp / 4;
+        sv += vc;
+        sop += vc;
       }
-      sv[t * vc + j] = v;
+      if (c + kStages < chunks) bar_arrive<kBarEmpty>(sb_, NC + 32);
+      bar_arrive<kBarOutFull>(b, NC + NS);
     }
-    __syncthreads();
-#pragma unroll 1
-    for (int t = 0; t < nt; ++t) {
-      const float vv = sv[t * vc + cl];
-      const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + part * R);
-      const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + part * R);
-      float acc = 0.0f;
+    if (live) {
 #pragma unroll
-      for (int i = 0; i < R / 4; ++i) {
-        const float4 kk = k4[i], qq = q4[i];
-        S[4 * i + 0] = fmaf(decay, S[4 * i + 0], kk.x * vv);
-        acc = fmaf(S[4 * i + 0], qq.x, acc);
-        S[4 * i + 1] = fmaf(decay, S[4 * i + 1], kk.y * vv);
-        acc = fmaf(S[4 * i + 1], qq.y, acc);
-        S[4 * i + 2] = fmaf(decay, S[4 * i + 2], kk.z * vv);
-        acc = fmaf(S[4 * i + 2], qq.z, acc);
-        S[4 * i + 3] = fmaf(decay, S[4 * i + 3], kk.w * vv);
-        acc = fmaf(S[4 * i + 3], qq.w, acc);
-      }
-      so[(part * kChunk + t) * vc + cl] = acc;
+      for (int i = 0; i < R; ++i)
+        if (i < dn) st[static_cast<int64_t>(i) * p.V] = (i & 1) ? S[i / 2].y : S[i / 2].x;
     }
-    __syncthreads();
-    // the parts of every output, added in ascending order
-    for (int idx = threadIdx.x; idx < nt * vc; idx += blockDim.x) {
-      const int t = idx / vc, j = idx % vc;
-      if (c0 + j < V) {
-        float sum = so[t * vc + j];
-        for (int q = 1; q < parts; ++q) sum += so[(q * kChunk + t) * vc + j];
-        p.out[static_cast<int64_t>(row0 + t0 + t) * p.H * V + h * V + c0 + j] = sum;
+  } else if (tid < NC + 32) {
+    // ---------------------------------------------------------------- the loads
+    const int lane = tid - NC;
+    const int du = p.D / VEC, vu = vn / VEC;          // (VEC == 4 only when D and the columns are multiples of four)
+    // a chunk's copies are requested before the chunks in front of it are waited for and announced
+    auto request = [&](int c) {
+      const int sb_ = c % kStages, nt = min(kChunk, len - c * kChunk);
+      if (c >= kStages) bar_sync<kBarEmpty>(sb_, NC + 32);
+      float* sq = smem + sb_ * stage;
+      float* sk = sq + kChunk * Dp;
+      float* sv = sk + kChunk * Dp;
+      for (int t = 0; t < nt; ++t) {
+        const float* src = p.proj + static_cast<int64_t>(row0 + c * kChunk + t) * p.width;
+        const float* gq = src + p.q_off + h * p.D;
+        const float* gk = src + p.k_off + h * p.D;
+        const float* gv = src + p.v_off + h * p.V + c0;
+        for (int u = lane; u < du; u += 32) {
+          if (VEC == 4) {
+            copy_async16(sq + t * Dp + 4 * u, gq + 4 * u);
+            copy_async16(sk + t * Dp + 4 * u, gk + 4 * u);
+          } else {
+            copy_async4(sq + t * Dp + u, gq + u);
+            copy_async4(sk + t * Dp + u, gk + u);
+          }
+        }
+        for (int u = lane; u < vu; u += 32) {
+          if (VEC == 4) copy_async16(sv + t * vc + 4 * u, gv + 4 * u);
+          else copy_async4(sv + t * vc + u, gv + u);
+        }
       }
+      copy_async_commit();
+    };
+    constexpr int kAhead = kStages - 1;
+    for (int c = 0; c < kAhead && c < chunks; ++c) request(c);
+    for (int c = 0; c < chunks; ++c) {
+      if (c + kAhead < chunks) request(c + kAhead);
+      const int pending = min(kAhead, chunks - 1 - c);      // younger chunks that may still be on their way
+      if (pending >= 2) copy_async_wait<2>();
+      else if (pending == 1) copy_async_wait<1>();
+      else copy_async_wait<0>();
+      bar_arrive<kBarFull>(c % kStages, NC + 32);
+    }
+  } else {
+    // ---------------------------------------------------------------- the outputs: parts added in ascending order
+    const int j = tid - NC - 32;                      // this thread's value column
+    for (int c = 0; c < chunks; ++c) {
+      const int b = c & 1, nt = min(kChunk, len - c * kChunk);
+      bar_sync<kBarOutFull>(b, NC + NS);
+      if (j < vn) {
+        const float* src = so + b * outs + j;
+        float* dst = p.out + static_cast<int64_t>(row0 + c * kChunk) * p.H * p.V + h * p.V + c0 + j;
+        for (int t = 0; t < nt; ++t) {
+          float sum = src[t * vc];
+          for (int q = 1; q < parts; ++q) sum += src[(q * kChunk + t) * vc];
+          dst[static_cast<int64_t>(t) * p.H * p.V] = sum;
+        }
+      }
+      if (c + 2 < chunks) bar_arrive<kBarOutEmpty>(b, NC + NS);
     }
   }
+}
+
+// The same for steps in which every entry brings one token (decoding): nothing is staged ahead and no loop runs; a CTA is
+// (entry, head, 32 value columns), its warps the parts. The state's loads are requested first, the token's q, k, v (partial
+// sums folded, silu) go to shared memory meanwhile. Same operations in the same order as lightning_scan_kernel: same bits.
+__global__ void __launch_bounds__(512, 2) lightning_step_kernel(const ScanParams p) {
+  extern __shared__ __align__(16) float smem[];
+  sb::grid_launch_dependents();
+  const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+  const int parts = blockDim.x >> 5, Dp = parts * R;
+  const int part = threadIdx.x >> 5, cl = threadIdx.x & 31;
+  float* sq = smem;            // [Dp]
+  float* sk = sq + Dp;         // [Dp]
+  float* sv = sk + Dp;         // [32]
+  float* so = sv + 32;         // [parts][32]
+  const int slot = p.meta[e], row = p.meta[p.meta_stride + e], pos0 = p.meta[3 * p.meta_stride + e];
+  const float decay = p.decay[h];
+  const bool live = c0 + cl < p.V;
+  const int dn = min(R, p.D - part * R);
+  float* st = p.state + ((static_cast<int64_t>(slot) * p.H + h) * p.D + part * R) * p.V + c0 + cl;
+  sb::grid_dependency_wait();
+  float2 S[R / 2];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const float v = (pos0 > 0 && live && i < dn) ? st[static_cast<int64_t>(i) * p.V] : 0.0f;
+    if (i & 1) S[i / 2].y = v;
+    else S[i / 2].x = v;
+  }
+  const float* src = p.proj + static_cast<int64_t>(row) * p.width;
+  for (int j = threadIdx.x; j < 2 * Dp + 32; j += blockDim.x) {
+    float v = 0.0f;
+    if (j < 2 * Dp) {
+      const bool is_k = j >= Dp;
+      const int d = is_k ? j - Dp : j;
+      if (d < p.D) v = silu(folded(src + (is_k ? p.k_off : p.q_off) + h * p.D + d, p.n_partials, p.partial_stride));
+    } else if (c0 + j - 2 * Dp < p.V) {
+      v = silu(folded(src + p.v_off + h * p.V + c0 + j - 2 * Dp, p.n_partials, p.partial_stride));
+    }
+    smem[j] = v;
+  }
+  __syncthreads();
+  TokenKQ x;
+  x.load(reinterpret_cast<const float4*>(sk + part * R), reinterpret_cast<const float4*>(sq + part * R));
+  so[part * 32 + cl] = scan_token(S, x, sv[cl], decay);
   if (live) {
 #pragma unroll
     for (int i = 0; i < R; ++i)
-      if (part * R + i < D) st[static_cast<int64_t>(i) * V] = S[i];
+      if (i < dn) st[static_cast<int64_t>(i) * p.V] = (i & 1) ? S[i / 2].y : S[i / 2].x;
+  }
+  __syncthreads();
+  if (part == 0 && live) {
+    float sum = so[cl];
+    for (int q = 1; q < parts; ++q) sum += so[q * 32 + cl];
+    p.out[static_cast<int64_t>(row) * p.H * p.V + h * p.V + c0 + cl] = sum;
+  }
+}
+
+// act[r, j] = silu(sum of the partial buffers at [r, j]) for the first `cols` columns of every row: what the recurrence
+// reads, made once for all of a long step's tokens instead of by every CTA that needs a token's keys and queries.
+__global__ void lightning_activate_kernel(const float* __restrict__ proj, int n_partials, int64_t partial_stride, int width,
+                                          float* __restrict__ act, int n, int cols) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int64_t total = static_cast<int64_t>(n) * cols;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols, j = i % cols;
+    act[i] = silu(folded(proj + r * width + j, n_partials, partial_stride));
   }
 }
 
@@ -173,30 +359,46 @@ __global__ void __launch_bounds__(1024) gated_rmsnorm_kernel(const float* __rest
 // The recurrence for every entry of a step. proj: the projection's partial sums [n_partials][n][width] (float32) with
 // q at column q_off (H D), k at k_off (H D), v at v_off (H V); meta: the step's entry records [4][meta_stride]
 // on the device; state [slots][H][D][V] float32; out [n][H V] float32.
+// act: scratch [n][q, k, v columns] float32. Steps in which an entry brings several tokens apply the activation in a kernel
+// of its own first; steps of single tokens apply it inside theirs (the same function on the same sums: the same bits).
 SB_EXPORT int sb_lightning_scan(const float* proj, int n_partials, int64_t partial_stride, int width, int q_off, int k_off, int v_off,
-                                const int32_t* meta, int meta_stride, int entries, const float* decay, float* state, float* out,
-                                int H, int D, int V, cudaStream_t stream) {
-  if (entries <= 0) return 0;
-  if (H <= 0 || D <= 0 || V <= 0 || D > 512) return sb::fail("sb_lightning_scan: heads %d, key size %d (at most 512), value size %d", H, D, V);
+                                const int32_t* meta, int meta_stride, int entries, int n, const float* decay, float* state, float* out,
+                                float* act, int H, int D, int V, cudaStream_t stream) {
+  if (entries <= 0 || n <= 0) return 0;
+  if (H <= 0 || D <= 0 || V <= 0 || D > 256) return sb::fail("sb_lightning_scan: heads %d, key size %d (at most 256), value size %d", H, D, V);
   if (n_partials < 1) return sb::fail("sb_lightning_scan: n_partials must be >= 1");
-  const int R = D <= 64 ? 16 : 32;
   const int parts = (D + R - 1) / R, Dp = parts * R;
-  // value columns a CTA: whole warps, at most 512 threads, and as few CTAs as still fill the device
+  // value columns a CTA: whole warps, at most 576 threads with the loading and storing warps, and as few CTAs as still fill the device
   const int v_warps = (V + 31) / 32;
-  int vw = min(min(v_warps, 512 / (32 * parts)), 4);
+  int vw = min(min(v_warps, (576 - 32) / (32 * parts + 32)), 2);
   const long long sms = sb::sm_count();
   while (vw > 1 && static_cast<long long>(entries) * H * ((v_warps + vw - 1) / vw) < 2 * sms) --vw;
-  ScanParams p{proj, n_partials, partial_stride, width, q_off, k_off, v_off, meta, meta_stride, decay, state, out, H, D, V, 32 * vw};
+  if (n == entries) {     // one token an entry (decoding): small CTAs, many of them, nothing staged ahead
+    ScanParams p{proj, n_partials, partial_stride, width, q_off, k_off, v_off, meta, meta_stride, decay, state, out, H, D, V, 32, 1, 0};
+    sb::launch_pdl(lightning_step_kernel, dim3(entries, H, v_warps), dim3(parts * 32), sizeof(float) * (2 * Dp + 32 + parts * 32), stream, p);
+    return sb::check_launch("sb_lightning_scan");
+  }
+  // steps with longer entries: the activation once for all tokens, then the recurrence
+  if (act == nullptr) return sb::fail("sb_lightning_scan: a step with an entry of several tokens needs the scratch for the activated sums");
+  const int cols = max(max(q_off + H * D, k_off + H * D), v_off + H * V);
+  {
+    const int64_t total = static_cast<int64_t>(n) * cols;
+    const int blocks = static_cast<int>((total + 255) / 256 < sms * 16 ? (total + 255) / 256 : sms * 16);
+    sb::launch_pdl(lightning_activate_kernel, dim3(blocks), dim3(256), 0, stream, proj, n_partials, partial_stride, width, act, n, cols);
+  }
+  ScanParams p{act, 1, 0, cols, q_off, k_off, v_off, meta, meta_stride, decay, state, out, H, D, V, 32 * vw, kChunk, 1};
   const dim3 grid(entries, H, (v_warps + vw - 1) / vw);
-  const int threads = parts * 32 * vw;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * kChunk * Dp + static_cast<size_t>(kChunk) * p.vc * (1 + parts));
+  const int threads = parts * 32 * vw + 32 + 32 * vw;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(kStages) * kChunk * (2 * Dp + p.vc) + static_cast<size_t>(2) * kChunk * p.vc * parts);
   if (smem > 200 * 1024) return sb::fail("sb_lightning_scan: key size %d does not fit shared memory", D);
-  if (R == 16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(lightning_scan_kernel<16>, grid, dim3(threads), smem, stream, p);
+  const bool vec = D % 4 == 0 && V % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(act) & 15) == 0 && cols % 4 == 0;
+  if (vec) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(lightning_scan_kernel<4>, grid, dim3(threads), smem, stream, p);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb::launch_pdl(lightning_scan_kernel<32>, grid, dim3(threads), smem, stream, p);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(lightning_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb::launch_pdl(lightning_scan_kernel<1>, grid, dim3(threads), smem, stream, p);
   }
   return sb::check_launch("sb_lightning_scan");
 }
@@ -226,14 +428,15 @@ SB_EXPORT int sb_gated_rmsnorm(const float* o, const float* proj, int n_partials
 
 // ------------------------------------------------------------------ operations of the native step program (step_ops.h)
 // i: 0 projection partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 q_off, 5 k_off,
-//    6 v_off, 7 decay (float32 [H]), 8 state, 9 out (float32 [n, H V]), 10 H, 11 D, 12 V
+//    6 v_off, 7 decay (float32 [H]), 8 state, 9 out (float32 [n, H V]), 10 H, 11 D, 12 V, 13 scratch for the activated sums
 SB_EXPORT int sb_op_lightning_scan(const SbOp* op, const SbStep* s, void* stream) {
   using namespace sbstep;
   if (s->n <= 0) return SB_OP_SKIPPED;
   const int P = partial_count(op->i[2], op->i[3], s->n);
   return sb_lightning_scan(ptr<const float>(op->i[0]), P, static_cast<int64_t>(s->n) * op->i[1], (int)op->i[1], (int)op->i[4], (int)op->i[5],
-                           (int)op->i[6], entry_meta(s), s->max_rows, s->entries, ptr<const float>(op->i[7]), ptr<float>(op->i[8]),
-                           ptr<float>(op->i[9]), (int)op->i[10], (int)op->i[11], (int)op->i[12], static_cast<cudaStream_t>(stream));
+                           (int)op->i[6], entry_meta(s), s->max_rows, s->entries, s->n, ptr<const float>(op->i[7]), ptr<float>(op->i[8]),
+                           ptr<float>(op->i[9]), ptr<float>(op->i[13]), (int)op->i[10], (int)op->i[11], (int)op->i[12],
+                           static_cast<cudaStream_t>(stream));
 }
 
 // i: 0 o (float32 [n, W]), 1 projection partial sums (flat), 2 their width, 3 K ranges S, 4 most tokens with a buffer per range,

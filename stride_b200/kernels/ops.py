@@ -91,28 +91,30 @@ def layernorm(h: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: fl
                    dtype_code(out.dtype), n, H, eps, _stream()))
 
 
-def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, partials=None) -> None:
-    """out[i] = [a[i] (+ partials[s, i] for every s, ascending); b[i]]: float32 [n, H] twice into [n, 2 H] of out's dtype."""
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, partials=None, clear_a: bool = False) -> None:
+    """out[i] = [a[i] (+ partials[s, i] for every s, ascending); b[i]]: float32 [n, H] twice into [n, 2 H] of out's dtype.
+    With `clear_a`, a is zero afterwards."""
     _cuda(a, b, out, partials)
-    lib, fn = _fn("elementwise", "sb_concat_rows", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    lib, fn = _fn("elementwise", "sb_concat_rows", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     n, H = a.shape
     S = 0 if partials is None else partials.shape[0]
     stride = 0 if partials is None else partials.stride(0)
-    _check(lib, fn(_ptr(a), _ptr(partials), S, stride, _ptr(b), _ptr(out), dtype_code(out.dtype), n, H, _stream()))
+    _check(lib, fn(_ptr(a), _ptr(partials), S, stride, _ptr(b), _ptr(out), dtype_code(out.dtype), n, H, int(clear_a), _stream()))
 
 
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, entry_meta: torch.Tensor, entries: int, decay: torch.Tensor,
-                   state: torch.Tensor, out: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> None:
+                   state: torch.Tensor, out: torch.Tensor, heads: int, key_dim: int, value_dim: int, act=None) -> None:
     """The decayed linear-attention recurrence for every entry of a step (csrc/lightning.cu). proj [S, n, width] float32:
     partial sums of the projection with q, k, v at the given columns; entry_meta [4, E] on the device; state
-    [slots, heads, key_dim, value_dim] float32 (read unless the entry starts at position 0, written back); out [n, heads * value_dim]."""
-    _cuda(proj, entry_meta, decay, state, out)
-    lib, fn = _fn("lightning", "sb_lightning_scan", [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-                                                    c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    [slots, heads, key_dim, value_dim] float32 (read unless the entry starts at position 0, written back); out [n, heads * value_dim].
+    `act`: float32 scratch of n * (columns of q, k, v) elements; with it a long step's activations are made by a kernel of their own."""
+    _cuda(proj, entry_meta, decay, state, out, act)
+    lib, fn = _fn("lightning", "sb_lightning_scan", [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     if proj.dim() == 2:
         proj = proj.unsqueeze(0)
     _check(lib, fn(_ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], q_off, k_off, v_off, _ptr(entry_meta), entry_meta.stride(0),
-                   entries, _ptr(decay), _ptr(state), _ptr(out), heads, key_dim, value_dim, _stream()))
+                   entries, proj.shape[1], _ptr(decay), _ptr(state), _ptr(out), _ptr(act), heads, key_dim, value_dim, _stream()))
 
 
 def gated_rmsnorm(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:

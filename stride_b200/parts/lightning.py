@@ -35,8 +35,8 @@ class LightningMixer(Mixer):
         decay = [float(d) for d in p["decay"]]
         if len(decay) != self.num_heads:
             raise ValueError(f"lightning: {len(decay)} decay factors for {self.num_heads} heads")
-        if self.key_dim > 512:
-            raise ValueError(f"lightning: key_dim {self.key_dim} exceeds 512, the most the recurrence kernel holds")
+        if self.key_dim > 256:
+            raise ValueError(f"lightning: key_dim {self.key_dim} exceeds 256, the most the recurrence kernel holds")
         self._decay_host = torch.tensor(decay, dtype=torch.float32)
         self.decay = None
         self.proj = self.o = self.gain = None
@@ -73,7 +73,8 @@ class LightningMixer(Mixer):
         n, ws, H, D, V = ctx.n, ctx.workspace, self.num_heads, self.key_dim, self.value_dim
         proj = self.proj.forward_partials(x, ws.raw("lightning.proj", (self.proj.partial_elems(ws.max_tokens),), torch.float32))
         o = ws.get("lightning.o", n, (H * V,), torch.float32)
-        ops.lightning_scan(proj, self.q_off, self.k_off, self.v_off, ctx.entry_meta, ctx.entry_meta.shape[1], self.decay, cache.state, o, H, D, V)
+        act = ws.raw("lightning.act", (ws.max_tokens * self.g_off,), torch.float32)
+        ops.lightning_scan(proj, self.q_off, self.k_off, self.v_off, ctx.entry_meta, ctx.entry_meta.shape[1], self.decay, cache.state, o, H, D, V, act)
         y = ws.get("lightning.y", n, (H * V,), ctx.act_dtype)
         ops.gated_rmsnorm(o, proj, self.g_off, self.gain, self.eps, y)
         self.o.forward_add(y, stream, ws.raw("lightning.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
@@ -84,8 +85,9 @@ class LightningMixer(Mixer):
         proj = ws.raw("lightning.proj", (self.proj.partial_elems(T),), torch.float32)
         S = self.proj.emit_partials(program, x, proj)
         o = ws.get("lightning.o", T, (H * V,), torch.float32)
+        act = ws.raw("lightning.act", (T * self.g_off,), torch.float32)
         program.add("lightning", "sb_op_lightning_scan", [proj, self.proj_width, S, program.few_tokens, self.q_off, self.k_off, self.v_off,
-                                                          self.decay, cache.state, o, H, D, V])
+                                                          self.decay, cache.state, o, H, D, V, act])
         y = ws.get("lightning.y", T, (H * V,), self.env.act_dtype)
         program.add("lightning", "sb_op_gated_rmsnorm", [o, proj, self.proj_width, S, program.few_tokens, self.g_off, self.gain, self.gain.dtype,
                                                          y, y.dtype, H * V], [self.eps])

@@ -2,7 +2,8 @@
 token and W a [hidden, 2 hidden] matrix whose first half of columns meets h. Models that run a group of layers
 several times put it in front of every pass, so that each pass sees the token itself beside what the pass before made
 of it. The two streams are laid side by side in the activation dtype (the stream's pending partial sums folded in on the
-way) and go through one matrix product that overwrites h."""
+way, and h set to zero behind the read) and go through one matrix product, whose K ranges' partial sums are left pending
+on the now empty stream like those of any other projection: the next norm adds them, h = 0 + (r0 + r1 + ..)."""
 from __future__ import annotations
 
 import torch
@@ -40,13 +41,13 @@ class EmbeddingMix(Rewrite):
         if ctx.embedding_output is None:
             raise RuntimeError("embedding_mix: the model did not keep the embedding output")
         both = ctx.workspace.get("reentry.both", ctx.n, (2 * self.hidden,), ctx.act_dtype)
-        ops.concat_rows(stream.h, ctx.embedding_output, both, partials=stream.take_pending())
-        self.linear.forward(both, stream.h)
+        ops.concat_rows(stream.h, ctx.embedding_output, both, partials=stream.take_pending(), clear_a=True)
+        self.linear.forward_add(both, stream, ctx.workspace.raw("reentry.partials", (self.linear.partial_elems(ctx.workspace.max_tokens),), torch.float32))
 
     def emit(self, program):
         ws = program.workspace
         both = ws.get("reentry.both", ws.max_tokens, (2 * self.hidden,), self.env.act_dtype)
         flat, S, _ = program.take_pending() or (None, 1, 0)
         program.add("elementwise", "sb_op_concat_rows", [program.h, flat, S, program.few_tokens, program.embedding_output, both, both.dtype,
-                                                          self.hidden])
-        self.linear.emit(program, both, program.h)
+                                                          self.hidden, 1])
+        self.linear.emit_add(program, both, ws.raw("reentry.partials", (self.linear.partial_elems(ws.max_tokens),), torch.float32))

@@ -69,11 +69,12 @@ def test_lightning_scan_kernel(H, D, V):
     q, k, v = (x[:, a:a + w].view(n, H, -1) for a, w in ((0, H * D), (H * D + 4, H * D), (2 * H * D + 8, H * V)))
     rows = [sum(lengths[:i]) for i in range(len(lengths))]
 
-    def launch(entries, proj_rows, st):
+    def launch(entries, proj_rows, st, scratch=True):
         meta = torch.tensor([[e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries], [e[3] for e in entries]],
                             dtype=torch.int32, device=DEV)
         out = torch.zeros(proj_rows.shape[1], H * V, device=DEV)
-        ops.lightning_scan(proj_rows.to(DEV), 0, H * D + 4, 2 * H * D + 8, meta, len(entries), decay.to(DEV), st, out, H, D, V)
+        act = torch.empty(proj_rows.shape[1] * width, device=DEV) if scratch else None
+        ops.lightning_scan(proj_rows.to(DEV), 0, H * D + 4, 2 * H * D + 8, meta, len(entries), decay.to(DEV), st, out, H, D, V, act)
         return out.cpu()
 
     whole = launch([(slots[i], rows[i], lengths[i], 0) for i in range(4)], proj, state)
@@ -109,7 +110,7 @@ def test_lightning_scan_keeps_a_far_token():
     decay = torch.tensor([0.995])
     meta = torch.tensor([[0], [0], [n], [0]], dtype=torch.int32, device=DEV)
     out, st = torch.zeros(n, V, device=DEV), torch.zeros(1, H, D, V, device=DEV)
-    ops.lightning_scan(raw.to(DEV), 0, D, 2 * D, meta, 1, decay.to(DEV), st, out, H, D, V)
+    ops.lightning_scan(raw.to(DEV), 0, D, 2 * D, meta, 1, decay.to(DEV), st, out, H, D, V, torch.empty(n * (2 * D + V), device=DEV))
     silu = torch.nn.functional.silu
     want = (0.995 ** (n - 1 - far)) * D * float(silu(torch.tensor(6.0))) * float(silu(torch.tensor(5.0))) * silu(torch.arange(1, V + 1).float())
     got = out[n - 1].cpu()
@@ -160,9 +161,11 @@ def test_concat_rows_and_embedding_copy():
     a, b, parts = torch.randn(9, 50, generator=g), torch.randn(9, 50, generator=g), torch.randn(3, 9, 50, generator=g)
     for dt in (torch.float32, torch.bfloat16):
         out = torch.empty(9, 100, dtype=dt, device=DEV)
-        ops.concat_rows(a.to(DEV), b.to(DEV), out, partials=parts.to(DEV))
+        ad = a.to(DEV)
+        ops.concat_rows(ad, b.to(DEV), out, partials=parts.to(DEV), clear_a=dt == torch.bfloat16)
         want = torch.cat([a + (parts[0] + parts[1] + parts[2]), b], dim=1).to(dt)
         assert torch.equal(out.cpu(), want)
+        assert torch.equal(ad.cpu(), torch.zeros_like(a) if dt == torch.bfloat16 else a)
     table = torch.randn(30, 64, generator=g).to(torch.bfloat16).to(DEV)
     tokens = torch.tensor([3, 29, 0], dtype=torch.int32, device=DEV)
     out, copy = torch.empty(3, 64, device=DEV), torch.empty(3, 64, device=DEV)
