@@ -63,7 +63,8 @@ class KeralornConfig:
     layers: tuple
     loop_start: int = 0
     loop_stop: int = 0
-    loop_times: int = 1          # (start == stop: no loop)
+    loop_times: int = 1          # (start == stop: no layer is inside the loop)
+    loop_declared: bool = False  # config.json has a 'loop' entry (its matrix may then be in the checkpoint even if no pass runs)
     max_positions: int = DEFAULT_MAX_POSITIONS
     eos_token_ids: tuple = ()
 
@@ -129,7 +130,7 @@ class KeralornConfig:
                 raise ConfigError(f"config.json: 'loop' {loop!r} does not fit {len(layers)} layers")
         eos = j.get("eos_token_id")
         eos = () if eos is None else tuple(eos) if isinstance(eos, list) else (int(eos),)
-        return KeralornConfig(vocab, width, eps, tuple(layers), start, stop, times, eos_token_ids=eos)
+        return KeralornConfig(vocab, width, eps, tuple(layers), start, stop, times, loop_declared=bool(loop), eos_token_ids=eos)
 
 
 def keralorn_model_spec(cfg: KeralornConfig) -> ModelSpec:
@@ -164,6 +165,9 @@ def keralorn_model_spec(cfg: KeralornConfig) -> ModelSpec:
             layers.append(LayerSpec("prenorm_mixer", mixer=mixer, mixer_norm=norm(p + "norm1")))
     L = len(layers)
     order = list(range(L))
+    if cfg.loop_declared and not cfg.has_loop:
+        # a loop without layers has no pass and so no re-entry; its matrix, if the checkpoint brings it, is read and not used
+        layers.append(LayerSpec("rewrite", rewrite=PartSpec("embedding_mix", {"hidden_size": W, "optional": True}, {"weight": "loop.in"})))
     if cfg.has_loop:
         # the re-entry of the embedding is a layer of its own kind, scheduled in front of every pass; every pass of
         # a layer is a schedule entry of its own and so has a cache or state of its own

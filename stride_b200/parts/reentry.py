@@ -16,7 +16,8 @@ from .spec import TensorPlan
 
 @register_part("rewrite", "embedding_mix")
 class EmbeddingMix(Rewrite):
-    """params: hidden_size. tensors: weight [hidden, 2 hidden]."""
+    """params: hidden_size, optional (True: the matrix may be absent, for a part that no schedule entry runs).
+    tensors: weight [hidden, 2 hidden]."""
     graph_safe = True
     reads_embedding = True
 
@@ -26,13 +27,15 @@ class EmbeddingMix(Rewrite):
         self.linear = None
 
     def tensor_plan(self):
-        return {self.spec.tensors["weight"]: TensorPlan((self.hidden, 2 * self.hidden))}
+        return {self.spec.tensors["weight"]: TensorPlan((self.hidden, 2 * self.hidden), optional=bool(self.spec.params.get("optional", False)))}
 
     def bind(self, tensors):
-        self.linear = Linear(tensors[self.spec.tensors["weight"]], self.env.compute_dtype)
+        weight = tensors.get(self.spec.tensors["weight"])
+        if weight is not None:
+            self.linear = Linear(weight, self.env.compute_dtype)
 
     def weight_bytes(self):
-        return self.linear.weight_bytes()
+        return self.linear.weight_bytes() if self.linear is not None else 0
 
     def kernel_libraries(self):
         return {"elementwise", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}

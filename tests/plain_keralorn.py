@@ -118,7 +118,7 @@ def layer_order(cfg) -> list:
         return list(range(L))
     a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
     order = list(range(a))
-    for _ in range(times):
+    for _ in range(times if b > a else 0):       # (a pass without layers has no first layer, and so no re-entry)
         order += [-1] + list(range(a, b))
     return order + list(range(b, L))
 

@@ -123,3 +123,14 @@ def test_plain_rotary_frequencies():
 def test_gelu_tanh_values():
     z = torch.tensor([-3.0, -1.0, 0.0, 0.5, 2.0])
     assert torch.allclose(plain.gelu_tanh(z), torch.nn.functional.gelu(z, approximate="tanh"), atol=1e-6)
+
+
+def test_a_loop_without_layers_has_no_pass():
+    cfg = copy.deepcopy(KERALORN_R)
+    cfg["loop"] = {"start": 2, "stop": 2, "times": 3}
+    spec = _spec(cfg)
+    assert [e.layer for e in spec.schedule] == [0, 1, 2] and plain.layer_order(cfg) == [0, 1, 2]
+    assert model_plan(cfg)["loop.in"].optional                 # the checkpoint may bring the matrix; nothing runs it
+    one = copy.deepcopy(KERALORN_P)
+    one["loop"]["times"] = 1
+    assert [e.layer for e in _spec(one).schedule] == [0, 4, 1, 2, 3]
