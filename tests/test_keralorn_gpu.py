@@ -388,3 +388,25 @@ def test_greedy_generation_through_the_entry_point(keralorn_dirs):
     cfgq = KERALORN["Q"][0]
     outs = bf.generate([random_tokens(cfgq["vocab"], n, n) for n in (70, 9, 33, 120, 64)], max_new_tokens=8)
     assert all(len(o.tokens) == 8 for o in outs)
+
+
+def test_command_line_generates_what_the_entry_point_generates(keralorn_dirs, tmp_path):
+    """bin/stride_cli on a Keralorn folder (greedy, float32 and bfloat16): the tokens of LLM.generate."""
+    import json
+    import subprocess
+    import sys
+    from conftest import ROOT
+    from stride_b200 import LLM
+    cfg = KERALORN["R"][0]
+    prompts = [random_tokens(cfg["vocab"], n, 900 + n) for n in (3, 50, 21)]
+    (tmp_path / "in.jsonl").write_text("".join(json.dumps({"id": i, "tokens": p}) + "\n" for i, p in enumerate(prompts)))
+    for path, dtype in (("exact", "float32"), ("tc", "bfloat16")):
+        out = tmp_path / f"out_{path}.jsonl"
+        subprocess.run([sys.executable, str(ROOT / "bin" / "stride_cli"), "--model", str(keralorn_dirs["R"]), "--input", str(tmp_path / "in.jsonl"),
+                        "--output", str(out), "--max-new", "6", "--concurrency", "2", "--max-rows", "32", "--prefill-chunk", "16",
+                        "--kv-blocks", "24", "--page-size", "8", "--max-slots", "4", "--max-context", "128", "--path", path], check=True, timeout=600)
+        got = [json.loads(l) for l in out.read_text().splitlines()]
+        llm = LLM(keralorn_dirs["R"], dtype=dtype, concurrency=2, max_rows=32, prefill_chunk=16, kv_pages=24, page_size=8, max_slots=4,
+                  max_context=128, device=DEV)
+        want = llm.generate(prompts, max_new_tokens=6)
+        assert [g["tokens"] for g in got] == [w.tokens for w in want] and all(g["finish"] == "length" for g in got)
