@@ -115,13 +115,14 @@ class LayerCache:
     page_size: int = 0
     state: Optional[torch.Tensor] = None        # [slots, *state_shape]
     writes: bool = True                         # False: the entry reads another entry's cache
+    parts: Optional[list] = None                # an entry that asked with a list of needs: one LayerCache per need, in order
 
 
 class CacheManager:
     def __init__(self, needs: list, *, device, max_slots: int, max_context: int, page_size: int = 64,
                  num_pages: Optional[int] = None, cache_bytes: Optional[int] = None, shuffle_seed: int = 0):
-        """`needs[i]` is the CacheNeed of schedule entry i, None, or ("shared", j) for an entry that
-        reads entry j's cache. `num_pages` is the pool size in pages of every group; alternatively
+        """`needs[i]` is the CacheNeed of schedule entry i, None, ("shared", j) for an entry that
+        reads entry j's cache, or a list of those for an entry whose mixer is several side by side. `num_pages` is the pool size in pages of every group; alternatively
         `cache_bytes` is divided among the groups in proportion to their bytes per page. A
         `shuffle_seed` other than 0 permutes the free lists, so that tests meet pages in every order."""
         if page_size <= 0:
@@ -143,7 +144,17 @@ class CacheManager:
         self.length = np.zeros(max_slots, dtype=np.int32)
         self.live = np.zeros(max_slots, dtype=np.uint8)
 
+        # A schedule entry whose mixer is several mixers side by side asks with a list of needs: each is kept under the
+        # key (entry, index in the list) exactly like a single entry's need, and the entry's LayerCache lists them as `parts`.
+        self.entry_parts: dict = {}     # schedule entry -> keys of its parts
+        flat = []
         for i, need in enumerate(needs):
+            if isinstance(need, list):
+                self.entry_parts[i] = [(i, k) for k in range(len(need))]
+                flat += [((i, k), sub) for k, sub in enumerate(need)]
+            else:
+                flat.append((i, need))
+        for i, need in flat:
             if need is None:
                 continue
             if isinstance(need, tuple) and need[0] == "shared":
@@ -275,7 +286,9 @@ class CacheManager:
             g.table_device[slot].copy_(g.table_pinned[slot], non_blocking=True)
 
     # ------------------------------------------------------------------ views
-    def layer_cache(self, entry: int) -> LayerCache:
+    def layer_cache(self, entry) -> LayerCache:
+        if entry in self.entry_parts:
+            return LayerCache(parts=[self.layer_cache(key) for key in self.entry_parts[entry]])
         src = self.entry_shared.get(entry, entry)
         lc = LayerCache(writes=entry not in self.entry_shared)
         if src in self.entry_group:

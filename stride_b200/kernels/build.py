@@ -43,6 +43,11 @@ SOURCES = {
     "attention_tc5": "attention_tc5.cu",
     "decode_chain": "decode_chain.cu",
     "lightning": "lightning.cu",
+    "branch": "branch.cu",
+    "feed_forward": "feed_forward.cu",
+    "sigmoid_attention": "sigmoid_attention.cu",
+    "gated_recurrence": "gated_recurrence.cu",
+    "rglru": "rglru.cu",
     "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-g1", "-shared", "-fPIC", "-fvisibility=hidden"]

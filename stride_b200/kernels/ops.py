@@ -403,3 +403,156 @@ def attention_tc5_status() -> int:
     lib = library("attention_tc5")
     lib.sb_attention_tc5_status.restype = c_int
     return lib.sb_attention_tc5_status()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Branches beside the residual stream, feed-forwards that are no plain gated product, attention without softmax, and
+# recurrences with a gate per channel (csrc/branch.cu, feed_forward.cu, sigmoid_attention.cu, gated_recurrence.cu, rglru.cu)
+
+def _partials(p):
+    """(pointer, count, stride) of partial sums [P, n, M] (a 2-D tensor counts as P = 1), or zeros for None."""
+    if p is None:
+        return 0, 0, 0
+    if p.dim() == 2:
+        p = p.unsqueeze(0)
+    return p.data_ptr(), p.shape[0], p.stride(0)
+
+
+def branch_fold(dst: torch.Tensor, a=None, a_partials=None, ca: float = 1.0, b=None, b_partials=None, cb: float = 1.0, gain=None) -> None:
+    """dst += gain * (ca * (a + sum of a_partials) + cb * (b + sum of b_partials)), all float32 [n, W]; a and b are zero afterwards."""
+    _cuda(dst, a, a_partials, b, b_partials, gain)
+    lib, fn = _fn("branch", "sb_branch_fold", [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_float, c_void_p, c_void_p, c_int, c_int64, c_float,
+                                               c_void_p, c_int, c_int, c_int, c_void_p])
+    n, W = dst.shape
+    pa, na, sa = _partials(a_partials)
+    pb, nb, sb = _partials(b_partials)
+    _check(lib, fn(_ptr(dst), _ptr(a), pa, na, sa, ca, _ptr(b), pb, nb, sb, cb, _ptr(gain), dtype_code(gain.dtype) if gain is not None else 0,
+                   n, W, _stream()))
+
+
+def row_scaled_add(dst: torch.Tensor, x: torch.Tensor, weights: torch.Tensor, first: int, count: int) -> None:
+    """dst[r, :] += (weights[r, first] + .. + weights[r, first + count - 1]) * x[r, :]."""
+    _cuda(dst, x, weights)
+    lib, fn = _fn("branch", "sb_row_scaled_add", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    n, W = dst.shape
+    _check(lib, fn(_ptr(dst), _ptr(x), dtype_code(x.dtype), _ptr(weights), weights.stride(0), first, count, n, W, _stream()))
+
+
+def polynorm(up: torch.Tensor, out: torch.Tensor, coefficients, eps: float) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row of z = the sum of `up` [P, n, F]; N(y) = y / sqrt(mean(y^2) + eps)."""
+    _cuda(up, out)
+    lib, fn = _fn("feed_forward", "sb_polynorm", [c_void_p, c_int, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+                                                   c_float, c_void_p])
+    p, P, stride = _partials(up)
+    n, F = out.shape
+    a, b, c, e = (float(v) for v in coefficients)
+    _check(lib, fn(p, P, stride, _ptr(out), dtype_code(out.dtype), n, F, a, b, c, e, eps, _stream()))
+
+
+def moe_route(logits: torch.Tensor, correction: torch.Tensor, weights: torch.Tensor, top: int, scale: float) -> None:
+    """weights[r, x] = softmax(logits[r])[x] / (sum over the chosen + 1e-20) * scale for the `top` experts with the largest
+    softmax + correction, 0 for the others."""
+    _cuda(logits, correction, weights)
+    lib, fn = _fn("feed_forward", "sb_moe_route", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    n, X = weights.shape
+    _check(lib, fn(_ptr(logits), logits.stride(0), _ptr(correction), dtype_code(correction.dtype), _ptr(weights), n, X, top, scale, _stream()))
+
+
+def moe_activate(up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, experts: int, ff: int) -> None:
+    """out[r, e ff + j] = weights[r, e] * relu(sum of up [P, n, E ff])^2."""
+    _cuda(up, weights, out)
+    lib, fn = _fn("feed_forward", "sb_moe_activate", [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(up)
+    _check(lib, fn(p, P, stride, _ptr(weights), weights.stride(0), _ptr(out), dtype_code(out.dtype), out.shape[0], experts, ff, _stream()))
+
+
+def qkv_rotate_append(qkv: torch.Tensor, positions, slots, cos_sin, rotary_dim: int, q_out, cache_layer, block_table, num_heads: int,
+                      num_kv_heads: int, key_dim: int, value_dim: int, write_kv: bool = True) -> None:
+    """Rotate q and k of `qkv` [P, n, Hq D + Hkv D + Hkv Dv] (partial sums added), store q, append k and v to the pages
+    [pages, 2, Hkv, page_size, >= max(D, Dv)]."""
+    _cuda(qkv, positions, slots, cos_sin, q_out, cache_layer, block_table)
+    lib, fn = _fn("sigmoid_attention", "sb_qkv_rotate_append",
+                  [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                   c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(qkv)
+    n = q_out.shape[0]
+    _check(lib, fn(p, P, stride, _ptr(positions), _ptr(slots), _ptr(cos_sin), rotary_dim, _ptr(q_out), dtype_code(q_out.dtype), _ptr(cache_layer),
+                   dtype_code(cache_layer.dtype), _ptr(block_table), block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0),
+                   cache_layer.stride(1), cache_layer.stride(2), n, num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4],
+                   int(write_kv), _stream()))
+
+
+def sigmoid_attention(q, out, cache_layer, block_table, positions, slots, bias, num_heads: int, num_kv_heads: int, key_dim: int,
+                      value_dim: int, window: int, scale: float) -> None:
+    """out[i] = sum over the visible keys j of sigmoid(scale q_i.k_j + bias[head]) v_j over the paged cache."""
+    _cuda(q, out, cache_layer, block_table, positions, slots, bias)
+    if not (q.dtype == out.dtype == cache_layer.dtype):
+        raise TypeError("sigmoid_attention takes q, out and cache of one dtype")
+    lib, fn = _fn("sigmoid_attention", "sb_sigmoid_attention",
+                  [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), dtype_code(q.dtype), _ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3],
+                   cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2), _ptr(positions), _ptr(slots), _ptr(bias), q.shape[0],
+                   num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4], window, scale, _stream()))
+
+
+def hgrn2_activate(proj: torch.Tensor, f_bias, lower, act: torch.Tensor, HD: int, HV: int) -> None:
+    """act [n, 3 HD + HV] = q | g | k | v from the sums of proj [P, n, 2 HD + HV] = q | f | v: q = silu, g = lower + (1 - lower) sigmoid(f + bias),
+    k = 1 - g, v as projected."""
+    _cuda(proj, f_bias, lower, act)
+    if f_bias.dtype != lower.dtype:
+        raise TypeError("hgrn2_activate takes the gate's bias and lower bound in one dtype")
+    lib, fn = _fn("gated_recurrence", "sb_hgrn2_activate", [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(proj)
+    _check(lib, fn(p, P, stride, _ptr(f_bias), _ptr(lower), dtype_code(lower.dtype), _ptr(act), act.shape[0], HD, HV, _stream()))
+
+
+def gated_scan(act: torch.Tensor, q_off: int, g_off: int, k_off: int, v_off: int, entry_meta: torch.Tensor, entries: int, state: torch.Tensor,
+               out: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> None:
+    """S <- diag(g) S + k v^T, o = S^T q for every entry of the step, token by token; state [slots, heads, key_dim, value_dim] float32."""
+    _cuda(act, entry_meta, state, out)
+    lib, fn = _fn("gated_recurrence", "sb_gated_scan", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                         c_int, c_int, c_int, c_void_p])
+    _check(lib, fn(_ptr(act), act.stride(0), q_off, g_off, k_off, v_off, _ptr(entry_meta), entry_meta.stride(0), entries, _ptr(state), _ptr(out),
+                   heads, key_dim, value_dim, _stream()))
+
+
+def group_rmsnorm(o: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, heads: int, value_dim: int) -> None:
+    """Every head's value_dim outputs RMS-normed on their own, times gain [value_dim]."""
+    _cuda(o, gain, out)
+    lib, fn = _fn("gated_recurrence", "sb_group_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(o), _ptr(gain), dtype_code(gain.dtype), _ptr(out), dtype_code(out.dtype), o.shape[0], heads, value_dim, eps, _stream()))
+
+
+def rglru_conv(proj: torch.Tensor, x_bias, taps, conv_bias, positions, slots, state: torch.Tensor, u: torch.Tensor) -> None:
+    """u = causal convolution per channel of x = (columns C.. of the sums of proj [P, n, 2 C]) + x_bias; taps [C, K], the last one on
+    the token itself; earlier inputs from the step's rows or from state [slots, K, C]."""
+    _cuda(proj, x_bias, taps, conv_bias, positions, slots, state, u)
+    lib, fn = _fn("rglru", "sb_rglru_conv", [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(proj)
+    n, C = u.shape
+    _check(lib, fn(p, P, stride, _ptr(x_bias), _ptr(taps), _ptr(conv_bias), dtype_code(taps.dtype), _ptr(positions), _ptr(slots), _ptr(state),
+                   _ptr(u), n, C, taps.shape[1], _stream()))
+
+
+def rglru_gates(gates: torch.Tensor, r_bias, i_bias, lam, y_bias, u, proj, a, d, y, blocks: int) -> None:
+    """a = exp(-8 sigmoid(gates_r + r_bias) softplus(lam)), d = sqrt(1 - a^2) sigmoid(gates_i + i_bias) u, y = gelu_tanh(proj_y + y_bias);
+    gates [n, blocks, 2, C / blocks]."""
+    _cuda(gates, r_bias, i_bias, lam, y_bias, u, proj, a, d, y)
+    lib, fn = _fn("rglru", "sb_rglru_gates", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_void_p,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(proj)
+    n, C = u.shape
+    _check(lib, fn(_ptr(gates), _ptr(r_bias), _ptr(i_bias), _ptr(lam), _ptr(y_bias), dtype_code(lam.dtype), _ptr(u), p, P, stride, _ptr(a), _ptr(d),
+                   _ptr(y), n, C, blocks, _stream()))
+
+
+def rglru_scan(a, d, y, proj, x_bias, entry_meta: torch.Tensor, entries: int, state: torch.Tensor, out: torch.Tensor, taps: int) -> None:
+    """S <- a S + d token by token for every entry of the step, out = S * y; writes S and the convolution's last inputs back to state."""
+    _cuda(a, d, y, proj, x_bias, entry_meta, state, out)
+    lib, fn = _fn("rglru", "sb_rglru_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int, c_int,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    p, P, stride = _partials(proj)
+    _check(lib, fn(_ptr(a), _ptr(d), _ptr(y), p, P, stride, _ptr(x_bias), dtype_code(x_bias.dtype), _ptr(entry_meta), entry_meta.stride(0), entries,
+                   _ptr(state), _ptr(out), dtype_code(out.dtype), out.shape[1], taps, _stream()))

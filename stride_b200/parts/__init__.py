@@ -1,9 +1,10 @@
-from .base import (Block, BuildEnv, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, Rewrite, part_class,
+from .base import (Block, BranchScale, BuildEnv, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, Rewrite, part_class,
                    register_part)
 from .context import ResidualStream, StepContext, Workspace
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorPlan
-from . import attention, block, ends, lightning, mlp, norm, reentry, rope  # register the built-in kinds
+from . import (attention, block, branch, ends, experts, hgrn2, lightning, mlp, norm, parallel, reentry, rglru, rope,  # register the built-in kinds
+               sigmoid_attention)
 from .model import DecoderModel
 
-__all__ = ["Block", "BuildEnv", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Rewrite", "part_class",
+__all__ = ["Block", "BranchScale", "BuildEnv", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Rewrite", "part_class",
            "register_part", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "TensorPlan", "DecoderModel", "ResidualStream", "StepContext", "Workspace"]

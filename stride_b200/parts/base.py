@@ -1,8 +1,8 @@
 """Interfaces of the parts a model is put together from, and the part registry.
 
 A part knows its own sizes and constants (from its `PartSpec`) and nothing about
-the model it sits in. Six categories exist: "norm", "position", "mixer",
-"feed_forward", "rewrite" and "block" (plus "embedding" and "head" at the ends of the model).
+the model it sits in. Seven categories exist: "norm", "position", "mixer",
+"feed_forward", "rewrite", "branch_scale" and "block" (plus "embedding" and "head" at the ends of the model).
 A new kind is one class registered under a category:
 
     @register_part("mixer", "my_kind")
@@ -29,7 +29,7 @@ from .spec import PartSpec, TensorPlan
 
 _REGISTRY: dict = {}
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "rewrite", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "rewrite", "branch_scale", "block", "embedding", "head")
 
 
 def register_part(category: str, kind: str):
@@ -144,7 +144,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_need(self) -> Optional[CacheNeed]:
+    def cache_need(self):
+        """A CacheNeed, None, or a list of CacheNeeds (a mixer made of several: its `LayerCache` then has `parts` in that order)."""
         return None
 
     def forward(self, ctx, x: torch.Tensor, stream, cache) -> None:
@@ -155,6 +156,16 @@ class Mixer(Part):
 class FeedForward(Part):
     def forward(self, ctx, x: torch.Tensor, stream) -> None:
         """Per-token transform: read `x` [n, hidden], add the result to `stream`."""
+        raise NotImplementedError
+
+
+class BranchScale(Part):
+    """What takes a sublayer's result from a branch buffer into the residual stream, scaled on the way (a layer scale).
+    A block that has one runs its mixer or feed-forward on a branch (a `ResidualStream` over a buffer that is zero between
+    uses) instead of the stream itself."""
+
+    def forward(self, ctx, branch, stream) -> None:
+        """stream.h += scale(branch.h + the branch's pending partial sums); the branch is empty afterwards."""
         raise NotImplementedError
 
 

@@ -1,6 +1,10 @@
 """RMSNorm: y = w * (x / sqrt(mean(x^2) + eps)), all in 32-bit
-(arhaamatiq/stride src/kernels.cu:119-200: the weight is a plain gain, eps sits inside the root)."""
+(arhaamatiq/stride src/kernels.cu:119-200: the weight is a plain gain, eps sits inside the root). With the parameter
+`offset` the stored vector is the gain's distance from it, w = offset + stored (designs that store the gain around zero
+have offset 1); the sum is made once, in 32-bit, when the weights are bound."""
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from .base import Norm, register_part
@@ -9,7 +13,7 @@ from .spec import TensorPlan
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps. tensors: weight."""
+    """params: size, eps, offset (0 by default). tensors: weight."""
     graph_safe = True
 
 
@@ -17,13 +21,16 @@ class RMSNorm(Norm):
         super().__init__(spec, env)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
         self.weight = None
 
     def tensor_plan(self):
-        return {self.spec.tensors["weight"]: TensorPlan((self.size,))}
+        return {self.spec.tensors["weight"]: TensorPlan((self.size,), zero_mean=self.offset != 0.0)}
 
     def bind(self, tensors):
         self.weight = tensors[self.spec.tensors["weight"]].contiguous()
+        if self.offset != 0.0:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
