@@ -152,7 +152,8 @@ def ganupel_model_spec(cfg: GanupelConfig) -> ModelSpec:
             a, g = l.left, l.right
             position = None
             if a.rot_dims:
-                position = PartSpec("rope", {"head_dim": a.dim, "rotary_dim": a.rot_dims, "theta": a.rot_base, "scaling": {"rope_type": "default"}})
+                position = PartSpec("rope", {"head_dim": a.dim, "rotary_dim": a.rot_dims, "theta": a.rot_base, "scaling": {"rope_type": "default"},
+                                             "exact_angles": True})
             left = PartSpec("sigmoid_attention", {"hidden_size": W, "num_heads": a.heads, "num_kv_heads": a.kv_heads, "key_dim": a.dim,
                                                   "value_dim": a.vdim, "window": a.window, "scale": a.scale, "position": position},
                             {"q": p + "mix.left.q", "k": p + "mix.left.k", "v": p + "mix.left.v", "o": p + "mix.left.o", "bias": p + "mix.left.pb"})

@@ -42,7 +42,9 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: dict) -> np.ndar
 
 @register_part("position", "rope")
 class RotaryEncoding(PositionEncoding):
-    """params: head_dim, rotary_dim (default head_dim), theta, scaling (dict with rope_type and its factors)."""
+    """params: head_dim, rotary_dim (default head_dim), theta, scaling (dict with rope_type and its factors),
+    exact_angles (False by default: frequencies and angles in 32-bit as above; True: frequency theta^(-2i/rotary_dim) and
+    angle in 64-bit, so that the table is the rounding of the exact cos and sin at every position)."""
     graph_safe = True
 
 
@@ -53,8 +55,14 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(p.get("rotary_dim", self.head_dim))
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim or self.rotary_dim <= 0:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and in 2..head_dim {self.head_dim}")
-        inv = inverse_frequencies(self.rotary_dim, float(p["theta"]), p.get("scaling") or {})
-        pos = np.arange(env.max_positions, dtype=np.float32)
-        angle = (inv[None, :] * pos[:, None]).astype(np.float32).astype(np.float64)
+        if p.get("exact_angles"):
+            if (p.get("scaling") or {}).get("rope_type", "default") != "default":
+                raise ValueError("rotary encoding: exact_angles goes with the default scaling only")
+            inv = np.array([math.pow(float(p["theta"]), -2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)], dtype=np.float64)
+            angle = inv[None, :] * np.arange(env.max_positions, dtype=np.float64)[:, None]
+        else:
+            inv = inverse_frequencies(self.rotary_dim, float(p["theta"]), p.get("scaling") or {})
+            pos = np.arange(env.max_positions, dtype=np.float32)
+            angle = (inv[None, :] * pos[:, None]).astype(np.float32).astype(np.float64)
         table = np.stack([np.cos(angle), np.sin(angle)], axis=-1).astype(np.float32)
         self.cos_sin = torch.from_numpy(table).to(env.device)   # [max_positions, rotary_dim / 2, 2]

@@ -3,6 +3,11 @@ batching, float64 arithmetic on the CPU. It shares no code with the engine; the 
 
 A model is (config dict, {tensor name: torch tensor}); weights are widened exactly. Notation: x [T, W] is the residual
 stream of one sequence whose tokens stand at positions 0..T-1; W_foo y means y @ W_foo.T.
+
+`rnd` (None or torch.bfloat16) rounds where an engine that serves in that precision may round: the inputs of the matrix
+products (normed activations, rotated q and cached k and v, the mixers' outputs in front of W_o, the feed-forwards'
+hidden activations). Everything the design wants in 32-bit stays unrounded. The difference between the two is the size
+of the rounding noise that the tests measure the bfloat16 engine by.
 """
 from __future__ import annotations
 
@@ -15,6 +20,10 @@ F = torch.float64
 
 def w(tensors, name):
     return tensors[name].to(F)
+
+
+def rounded(x, rnd):
+    return x if rnd is None else x.to(rnd).to(F)
 
 
 def rms(x, eps):
@@ -48,7 +57,7 @@ def rotate(x, dims, base):
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
 
 
-def sigmoid_window_attention(h, tensors, prefix, m):
+def sigmoid_window_attention(h, tensors, prefix, m, rnd=None):
     """Grouped heads, rotated q and k, a window of `mask.size` positions, and instead of softmax an independent weight
     sigmoid(score + bias_head) per visible key."""
     T = h.shape[0]
@@ -57,7 +66,8 @@ def sigmoid_window_attention(h, tensors, prefix, m):
     k = (h @ w(tensors, prefix + "k").T).view(T, G, D)
     v = (h @ w(tensors, prefix + "v").T).view(T, G, V)
     rot = m.get("rot") or {"dims": 0, "base": 1.0}
-    q, k = rotate(q, rot["dims"], rot["base"]), rotate(k, rot["dims"], rot["base"])
+    q, k = rounded(rotate(q, rot["dims"], rot["base"]), rnd), rounded(rotate(k, rot["dims"], rot["base"]), rnd)
+    v = rounded(v, rnd)
     pb = w(tensors, prefix + "pb")
     window = (m.get("mask") or {}).get("size", 0)
     i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
@@ -68,10 +78,10 @@ def sigmoid_window_attention(h, tensors, prefix, m):
         score = (q[:, head] @ k[:, g].T) * m["scale"]
         weight = torch.sigmoid(score + pb[head]) * seen
         out[:, head] = weight @ v[:, g]
-    return out.reshape(T, H * V) @ w(tensors, prefix + "o").T
+    return rounded(out.reshape(T, H * V), rnd) @ w(tensors, prefix + "o").T
 
 
-def hgrn2(h, tensors, prefix, m, eps):
+def hgrn2(h, tensors, prefix, m, eps, rnd=None):
     """Linear attention whose forget gate f also writes: S <- diag(f) S + (1 - f) v^T, o = S^T q."""
     T = h.shape[0]
     H, D, V = m["heads"], m["dim"], m["vdim"]
@@ -85,12 +95,12 @@ def hgrn2(h, tensors, prefix, m, eps):
         S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
         out[t] = torch.einsum("hdv,hd->hv", S, q[t])
     out = rms(out, eps) * w(tensors, prefix + "norm")
-    return out.reshape(T, H * V) @ w(tensors, prefix + "o").T
+    return rounded(out.reshape(T, H * V), rnd) @ w(tensors, prefix + "o").T
 
 
-def parallel_mixer(h, tensors, prefix, m, eps):
-    left = sigmoid_window_attention(h, tensors, prefix + "left.", m["left"])
-    right = hgrn2(h, tensors, prefix + "right.", m["right"], eps)
+def parallel_mixer(h, tensors, prefix, m, eps, rnd=None):
+    left = sigmoid_window_attention(h, tensors, prefix + "left.", m["left"], rnd)
+    right = hgrn2(h, tensors, prefix + "right.", m["right"], eps, rnd)
     return m["left_scale"] * left + m["right_scale"] * right
 
 
@@ -104,7 +114,7 @@ def causal_conv(x, taps, bias):
     return out
 
 
-def rglru(h, tensors, prefix, m):
+def rglru(h, tensors, prefix, m, rnd=None):
     """The recurrent block with a real-gated linear recurrent unit."""
     T, C, B = h.shape[0], m["width"], m["blocks"]
     y = gelu_tanh(h @ w(tensors, prefix + "y").T + w(tensors, prefix + "y.b"))
@@ -120,17 +130,17 @@ def rglru(h, tensors, prefix, m):
     for t in range(T):
         S = a[t] * S + drive[t]
         out[t] = S
-    return (out * y) @ w(tensors, prefix + "o").T
+    return rounded(out * y, rnd) @ w(tensors, prefix + "o").T
 
 
-def polynorm_feed_forward(h, tensors, prefix, eps):
+def polynorm_feed_forward(h, tensors, prefix, eps, rnd=None):
     z = h @ w(tensors, prefix + "up").T
     a, b, c, e = w(tensors, prefix + "act").tolist()
     act = a * rms(z, eps) + b * rms(z ** 2, eps) + c * rms(z ** 3, eps) + e
-    return act @ w(tensors, prefix + "down").T
+    return rounded(act, rnd) @ w(tensors, prefix + "down").T
 
 
-def routed_feed_forward(h, tensors, prefix, mlp):
+def routed_feed_forward(h, tensors, prefix, mlp, rnd=None):
     r = mlp["router"]
     E, I, top = r["experts"], r.get("identity", 0), r["top"]
     s = torch.softmax(h @ w(tensors, prefix + "router").T, dim=-1)             # [T, E + I]
@@ -145,38 +155,38 @@ def routed_feed_forward(h, tensors, prefix, mlp):
                 out[t] += g * h[t]
             else:
                 z = torch.relu(h[t] @ w(tensors, f"{prefix}e{e}.up").T) ** 2
-                out[t] += g * (z @ w(tensors, f"{prefix}e{e}.down").T)
+                out[t] += rounded(g * z, rnd) @ w(tensors, f"{prefix}e{e}.down").T
     return out
 
 
-def layer(x, tensors, i, spec, eps):
+def layer(x, tensors, i, spec, eps, rnd=None):
     p = f"l{i}."
-    h = offset_rms_norm(x, w(tensors, p + "norm1"), eps)
+    h = rounded(offset_rms_norm(x, w(tensors, p + "norm1"), eps), rnd)
     if spec["type"] == "parallel":
-        mixed = parallel_mixer(h, tensors, p + "mix.", spec["mixer"], eps)
+        mixed = parallel_mixer(h, tensors, p + "mix.", spec["mixer"], eps, rnd)
     elif spec["type"] == "rglru":
-        mixed = rglru(h, tensors, p + "mix.", spec["mixer"])
+        mixed = rglru(h, tensors, p + "mix.", spec["mixer"], rnd)
     else:
         raise ValueError(spec["type"])
     x = x + mixed * w(tensors, p + "ls1")
     mlp = spec.get("mlp")
     if mlp is not None:
-        h = offset_rms_norm(x, w(tensors, p + "norm2"), eps)
+        h = rounded(offset_rms_norm(x, w(tensors, p + "norm2"), eps), rnd)
         if mlp["kind"] == "dense":
-            y = polynorm_feed_forward(h, tensors, p + "mlp.", eps)
+            y = polynorm_feed_forward(h, tensors, p + "mlp.", eps, rnd)
         else:
-            y = routed_feed_forward(h, tensors, p + "mlp.", mlp)
+            y = routed_feed_forward(h, tensors, p + "mlp.", mlp, rnd)
         x = x + y * w(tensors, p + "ls2")
     return x
 
 
-def forward(config, tensors, tokens, keep_layers=False):
+def forward(config, tensors, tokens, rnd=None, keep_layers=False):
     """Logits [T, vocab] (float64) of one sequence; with keep_layers also the stream after every layer."""
     eps = config["norm"]["eps"]
     x = w(tensors, "embed")[torch.as_tensor(tokens, dtype=torch.long)]
     streams = []
     for i, spec in enumerate(config["layers"]):
-        x = layer(x, tensors, i, spec, eps)
+        x = layer(x, tensors, i, spec, eps, rnd)
         streams.append(x)
-    logits = offset_rms_norm(x, w(tensors, "final.norm"), eps) @ w(tensors, "head").T
+    logits = rounded(offset_rms_norm(x, w(tensors, "final.norm"), eps), rnd) @ w(tensors, "head").T
     return (logits, streams) if keep_layers else logits
