@@ -341,6 +341,19 @@ def _keralorn_config(width: int, ff: int, vocab: int, pairs: int, window: int) -
             "loop": {"start": 0, "stop": 2 * pairs, "times": 1}}
 
 
+def _ganupel_config(width: int, ff: int, vocab: int, pairs: int, window: int) -> dict:
+    """`pairs` times (recurrent block with a dense PolyNorm feed-forward; sigmoid attention beside HGRN2 with routed experts): the
+    attention has the heads of the Llama 3.2 1B layer, HGRN2 16 heads of 128 x 128, the recurrent block `width` channels in
+    blocks of 128, and the routed feed-forward eight experts of ff / 4 and one identity expert, two chosen."""
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}, "mlp": {"kind": "dense", "ff": ff}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": window},
+                              "rot": {"dims": 64, "base": 500000.0}},
+                     "right": {"heads": width // 128, "dim": 128, "vdim": 128}, "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "identity": 1, "top": 2, "scale": 1.0}}}
+    return {"architecture": "Ganupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": [rec, par] * pairs}
+
+
 def design_compare(a) -> int:
     """Keralorn at layer sizes of a real model beside LlamaForCausalLM with as many layers of the same width, heads and
     feed-forward (random weights, bfloat16 engine): a prompt of 2,048 tokens in one step, decode steps at batch 8 and 64
@@ -355,8 +368,10 @@ def design_compare(a) -> int:
     llama = _llama(width, ff, layers, width // 64, width // 256, 64, False, 32.0, context)
     llama["vocab_size"] = vocab
     configs = {"keralorn": _keralorn_config(width, ff, vocab, pairs, 1024), "llama": llama}
+    if a.design == "ganupel":      # beside the closest design (a recurrence with a state per request and windowed attention) and Llama
+        configs = {"ganupel": _ganupel_config(width, ff, vocab, pairs, 1024), **configs}
     gen = torch.Generator().manual_seed(3)
-    out = {"design": "keralorn", "beside": "LlamaForCausalLM", "width": width, "ff": ff, "layers": layers, "vocab": vocab,
+    out = {"design": a.design, "beside": "LlamaForCausalLM" if a.design == "keralorn" else "Keralorn, LlamaForCausalLM", "width": width, "ff": ff, "layers": layers, "vocab": vocab,
            "dtype": "bf16", "data": "synthetic (random weights and tokens)", "peaks": pk,
            "l2": "weights and caches of a step exceed the 126 MB L2; the kernel timings flush L2 between launches"}
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
@@ -434,6 +449,11 @@ def design_compare(a) -> int:
         del eng
         torch.cuda.empty_cache()
 
+    if a.design == "ganupel":
+        out["kernels"] = _ganupel_kernels(timed, pk, width, ff)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
     # Keralorn's own kernels alone, beside the like kernel of Llama where there is one
     H, D, V = width // 128, 128, 128
     kern = {}
@@ -471,6 +491,92 @@ def design_compare(a) -> int:
     return 0
 
 
+def _ganupel_kernels(timed, pk: dict, width: int, ff: int) -> dict:
+    """Ganupel's own kernels alone (L2 flushed between launches), each beside the like kernel of Keralorn or Llama."""
+    import torch
+    from stride_b200.kernels import ops
+    dev, kern = "cuda", {}
+    hbm = pk["hbm_gbs"] * 1e9
+
+    def record(label, ms, moved=None, flops=None, **more):
+        r = {"ms": round(ms, 4)}
+        if moved is not None:
+            r.update(gb_s=round(moved / ms / 1e6, 1), hbm_fraction_of_measured=round(moved / (ms * 1e-3) / hbm, 3))
+        if flops is not None:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+        r.update(more)
+        kern[label] = r
+
+    # the two recurrences, as prompts and as decode steps, beside the decayed recurrence of Keralorn on the same sizes
+    H, D, V = width // 128, 128, 128
+    for label, entries, length in (("prefill_2048", 1, 2048), ("prefill_8x2048", 8, 2048), ("decode_b64", 64, 1), ("decode_b512", 512, 1)):
+        n = entries * length
+        meta = torch.tensor([list(range(entries)), [e * length for e in range(entries)], [length] * entries, [0 if length > 1 else 7] * entries],
+                            dtype=torch.int32, device=dev)
+        act = torch.rand(n, 3 * H * D + H * V, device=dev)
+        state = torch.zeros(entries + 1, H, D, V, device=dev)
+        o = torch.empty(n, H * V, device=dev)
+        ms = timed(lambda: ops.gated_scan(act, 0, H * D, 2 * H * D, 3 * H * D, meta, entries, state, o, H, D, V), 5, clear=True)
+        moved = 4.0 * (n * (3 * H * D + H * V) + n * H * V + (2 if length == 1 else 1) * entries * H * D * V)
+        record("gated_scan_" + label, ms, moved, 5.0 * n * H * D * V)
+        proj = torch.randn(1, n, 2 * H * D + 2 * H * V, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        scratch = torch.empty(n * (2 * H * D + H * V), device=dev)
+        ms = timed(lambda: ops.lightning_scan(proj, 0, H * D, 2 * H * D, meta, entries, decay, state, o, H, D, V, scratch), 5, clear=True)
+        record("keralorn_scan_" + label, ms, 4.0 * (n * (2 * H * D + H * V) + n * H * V + (2 if length == 1 else 1) * entries * H * D * V),
+               5.0 * n * H * D * V)
+        C, K = width, 4
+        a_, d_, y_ = (torch.rand(n, C, device=dev) for _ in range(3))
+        pr = torch.randn(1, n, 2 * C, device=dev)
+        xb = torch.zeros(C, device=dev)
+        rec = torch.zeros(entries + 1, K, C, device=dev)
+        out = torch.empty(n, C, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.rglru_scan(a_, d_, y_, pr, xb, meta, entries, rec, out, K), 5, clear=True)
+        record("rglru_scan_" + label, ms, n * C * 14.0 + entries * K * C * 8.0)
+    # attention: a prompt of 2,048 tokens and decode steps over 1,024 cached tokens in the window
+    Hq, G, Dh, page, window = width // 64, width // 256, 64, 64, 1024
+    for label, entries, length, past in (("prefill_2048", 1, 2048, 0), ("decode_b64", 64, 1, 1500)):
+        n, per = entries * length, (past + length + page - 1) // page
+        pages = torch.randn(entries * per + 1, 2, G, page, Dh, device=dev).to(torch.bfloat16)
+        table = torch.arange(entries * per, dtype=torch.int32, device=dev).view(entries, per)
+        pos = torch.tensor([past + t for _ in range(entries) for t in range(length)], dtype=torch.int32, device=dev)
+        slot = torch.tensor([e for e in range(entries) for _ in range(length)], dtype=torch.int32, device=dev)
+        q = torch.randn(n, Hq * Dh, device=dev).to(torch.bfloat16)
+        o = torch.empty_like(q)
+        bias = torch.zeros(Hq, device=dev)
+        meta = torch.tensor([list(range(entries)), [e * length for e in range(entries)], [length] * entries, [past] * entries],
+                            dtype=torch.int32, device=dev)
+        keys = sum(min(window, past + t + 1) for t in range(length)) * entries
+        moved = (2.0 * entries * G * min(window, past + 1) * Dh * 2 + n * Hq * Dh * 4) if length == 1 else None
+        ms = timed(lambda: ops.sigmoid_attention_tiles(q, o, pages, table, meta, entries, bias, Hq, G, Dh, Dh, window, 0.125), 5, clear=True)
+        record("sigmoid_attention_" + label, ms, flops=4.0 * keys * Hq * Dh, moved=moved,
+               fraction_of_measured_bf16=round(6.0 * keys * Hq * Dh / ms / 1e9 / pk["bf16_tflops"], 4))
+        ms = timed(lambda: ops.sigmoid_attention(q, o, pages, table, pos, slot, bias, Hq, G, Dh, Dh, window, 0.125), 3, clear=True)
+        record("sigmoid_attention_block_per_token_" + label, ms, flops=4.0 * keys * Hq * Dh, moved=moved)
+    # between the products of the feed-forwards
+    for n in (64, 2048):
+        up = torch.randn(1, n, ff, device=dev)
+        z = torch.empty(n, ff, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.polynorm(up, z, (0.5, 0.3, 0.2, 0.0), 1e-5), 5, clear=True)
+        record(f"polynorm_{n}", ms, n * ff * 6.0)
+        E, F = 8, ff // 4
+        upe = torch.randn(1, n, E * F, device=dev)
+        w = torch.zeros(n, E + 1, device=dev)
+        w[:, :2] = 0.5
+        ze = torch.empty(n, E * F, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.moe_activate(upe, w, ze, E, F), 5, clear=True)
+        record(f"moe_activate_{n}", ms, n * E * F * 2.0 + n * 2 * F * 4.0)
+        h = torch.randn(n, width, device=dev)
+        br = torch.randn(n, width, device=dev)
+        parts = torch.randn(2, n, width, device=dev)
+        gain = torch.ones(width, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.branch_fold(h, a=br, a_partials=parts, gain=gain), 5, clear=True)
+        x = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+        ms_r = timed(lambda: ops.rmsnorm(h, gain, 1e-5, x, partials=parts), 5, clear=True)
+        record(f"branch_fold_{n}", ms, n * width * 24.0, rmsnorm_with_two_partials_ms=round(ms_r, 4))
+    return kern
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -481,8 +587,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="1b: the decode step (default); 3b, 8b: serving runs")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64, float32 and prefill measurements")
-    ap.add_argument("--design", default="", choices=["", "keralorn"],
-                    help="keralorn: prefill and decode of that design beside a Llama of equal layer sizes, and its own kernels alone")
+    ap.add_argument("--design", default="", choices=["", "keralorn", "ganupel"],
+                    help="keralorn: prefill and decode of that design beside a Llama of equal layer sizes, and its own kernels alone; "
+                         "ganupel: the same beside Keralorn and Llama")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)

@@ -27,56 +27,96 @@ struct Source {
   float c;
 };
 
-__device__ __forceinline__ float source_value(const Source& s, int64_t i) {
-  float v = 0.0f;
+// One element of a branch: its buffer (zero behind the read) plus its partial sums, h + (p0 + p1 + ..).
+template <class V>
+__device__ __forceinline__ V zero_of();
+template <>
+__device__ __forceinline__ float zero_of<float>() { return 0.0f; }
+template <>
+__device__ __forceinline__ float4 zero_of<float4>() { return make_float4(0.0f, 0.0f, 0.0f, 0.0f); }
+__device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float4 add(float4 a, float4 b) { return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w)); }
+__device__ __forceinline__ float mul(float a, float c) { return __fmul_rn(a, c); }
+__device__ __forceinline__ float4 mul(float4 a, float c) { return make_float4(__fmul_rn(a.x, c), __fmul_rn(a.y, c), __fmul_rn(a.z, c), __fmul_rn(a.w, c)); }
+__device__ __forceinline__ float4 mul(float4 a, float4 c) { return make_float4(__fmul_rn(a.x, c.x), __fmul_rn(a.y, c.y), __fmul_rn(a.z, c.z), __fmul_rn(a.w, c.w)); }
+
+template <class V>
+__device__ __forceinline__ V source_value(const Source& s, int64_t i) {      // i in units of V
+  V v = zero_of<V>();
   if (s.h != nullptr) {
-    v = s.h[i];
-    s.h[i] = 0.0f;
+    V* h = reinterpret_cast<V*>(s.h) + i;
+    v = *h;
+    *h = zero_of<V>();
   }
   if (s.partials != nullptr && s.n_partials > 0) {
-    float part[kInFlight];
+    const V* p = reinterpret_cast<const V*>(s.partials) + i;
+    const int64_t stride = s.stride / static_cast<int64_t>(sizeof(V) / sizeof(float));
+    V part[kInFlight];
 #pragma unroll
     for (int k = 0; k < kInFlight; ++k)
-      if (k < s.n_partials) part[k] = s.partials[k * s.stride + i];
-    float sum = part[0];
+      if (k < s.n_partials) part[k] = p[k * stride];
+    V sum = part[0];
 #pragma unroll
     for (int k = 1; k < kInFlight; ++k)
-      if (k < s.n_partials) sum += part[k];
-    for (int k = kInFlight; k < s.n_partials; ++k) sum += s.partials[k * s.stride + i];
-    v = s.h != nullptr ? v + sum : sum;
+      if (k < s.n_partials) sum = add(sum, part[k]);
+    for (int k = kInFlight; k < s.n_partials; ++k) sum = add(sum, p[k * stride]);
+    v = s.h != nullptr ? add(v, sum) : sum;
   }
   return v;
 }
 
 template <class TG>
-__global__ void branch_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ gain, int64_t total, int W) {
+__device__ __forceinline__ float4 gain4(const TG* gain, int c);
+template <>
+__device__ __forceinline__ float4 gain4<float>(const float* gain, int c) { return *reinterpret_cast<const float4*>(gain + c); }
+template <>
+__device__ __forceinline__ float4 gain4<bf16>(const bf16* gain, int c) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(gain + c);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+
+// A block per row. VEC: the width is a multiple of four and every buffer 16-byte aligned: four elements a thread and request.
+// The scalar form does the same operations on the same operands: equal bits.
+template <class TG, bool VEC>
+__global__ void __launch_bounds__(256) branch_fold_kernel(float* __restrict__ dst, Source a, Source b, const TG* __restrict__ gain, int W) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float v = __fmul_rn(a.c, source_value(a, i));
-    if (b.h != nullptr || b.partials != nullptr) v = __fadd_rn(v, __fmul_rn(b.c, source_value(b, i)));
-    if (gain != nullptr) v = __fmul_rn(v, sb::widen(gain[i % W]));
-    dst[i] = __fadd_rn(dst[i], v);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * W;
+  const bool two = b.h != nullptr || b.partials != nullptr;
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      const int64_t i = (row + c) / 4;
+      float4 v = mul(source_value<float4>(a, i), a.c);
+      if (two) v = add(v, mul(source_value<float4>(b, i), b.c));
+      if (gain != nullptr) v = mul(v, gain4<TG>(gain, c));
+      float4* d = reinterpret_cast<float4*>(dst) + i;
+      *d = add(*d, v);
+    }
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const int64_t i = row + c;
+      float v = mul(source_value<float>(a, i), a.c);
+      if (two) v = add(v, mul(source_value<float>(b, i), b.c));
+      if (gain != nullptr) v = mul(v, sb::widen(gain[c]));
+      dst[i] = add(dst[i], v);
+    }
   }
 }
 
 template <class TX>
-__global__ void row_scaled_add_kernel(float* __restrict__ dst, const TX* __restrict__ x, const float* __restrict__ w, int ldw, int first,
-                                      int count, int64_t total, int W) {
+__global__ void __launch_bounds__(256) row_scaled_add_kernel(float* __restrict__ dst, const TX* __restrict__ x, const float* __restrict__ w, int ldw,
+                                                             int first, int count, int W) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / W;
-    float g = 0.0f;
-    for (int k = 0; k < count; ++k) g += w[r * ldw + first + k];
-    if (g != 0.0f) dst[i] = fmaf(g, sb::widen(x[i]), dst[i]);
-  }
+  const int64_t r = blockIdx.x;
+  float g = 0.0f;
+  for (int k = 0; k < count; ++k) g += w[r * ldw + first + k];
+  if (g == 0.0f) return;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) dst[r * W + c] = fmaf(g, sb::widen(x[r * W + c]), dst[r * W + c]);
 }
 
-inline int grid_for(int64_t total) {
-  const int64_t blocks = (total + 255) / 256, most = static_cast<int64_t>(sb::sm_count()) * 16;
-  return static_cast<int>(blocks < most ? blocks : most);
-}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
 
@@ -84,25 +124,31 @@ SB_EXPORT int sb_branch_fold(float* dst, float* a, const float* pa, int na, int6
                              float cb, const void* gain, int gain_dtype, int n, int W, cudaStream_t stream) {
   if (n <= 0 || W <= 0) return 0;
   if (a == nullptr && pa == nullptr) return sb::fail("sb_branch_fold: the first branch has neither a buffer nor partial sums");
-  const int64_t total = static_cast<int64_t>(n) * W;
   const Source A{a, pa, pa ? na : 0, sa, ca}, B{b, pb, pb ? nb : 0, sb_, cb};
-  if (gain == nullptr || gain_dtype == 0)
-    sb::launch_pdl(branch_fold_kernel<float>, dim3(grid_for(total)), dim3(256), 0, stream, dst, A, B, static_cast<const float*>(gain), total, W);
-  else if (gain_dtype == 1)
-    sb::launch_pdl(branch_fold_kernel<bf16>, dim3(grid_for(total)), dim3(256), 0, stream, dst, A, B, static_cast<const bf16*>(gain), total, W);
-  else
+  const bool vec = W % 4 == 0 && aligned16(dst) && aligned16(a) && aligned16(pa) && aligned16(b) && aligned16(pb) && aligned16(gain) &&
+                   sa % 4 == 0 && sb_ % 4 == 0;
+  const int threads = W >= 1024 ? 256 : 128;
+#define SB_FOLD(TG, VEC) sb::launch_pdl(branch_fold_kernel<TG, VEC>, dim3(n), dim3(threads), 0, stream, dst, A, B, static_cast<const TG*>(gain), W)
+  if (gain == nullptr || gain_dtype == 0) {
+    if (vec) SB_FOLD(float, true);
+    else SB_FOLD(float, false);
+  } else if (gain_dtype == 1) {
+    if (vec) SB_FOLD(bf16, true);
+    else SB_FOLD(bf16, false);
+  } else {
     return sb::fail("sb_branch_fold: unsupported gain dtype %d", gain_dtype);
+  }
+#undef SB_FOLD
   return sb::check_launch("sb_branch_fold");
 }
 
 SB_EXPORT int sb_row_scaled_add(float* dst, const void* x, int x_dtype, const float* w, int ldw, int first, int count, int n, int W,
                                 cudaStream_t stream) {
   if (n <= 0 || W <= 0 || count <= 0) return 0;
-  const int64_t total = static_cast<int64_t>(n) * W;
   if (x_dtype == 0)
-    sb::launch_pdl(row_scaled_add_kernel<float>, dim3(grid_for(total)), dim3(256), 0, stream, dst, static_cast<const float*>(x), w, ldw, first, count, total, W);
+    sb::launch_pdl(row_scaled_add_kernel<float>, dim3(n), dim3(256), 0, stream, dst, static_cast<const float*>(x), w, ldw, first, count, W);
   else if (x_dtype == 1)
-    sb::launch_pdl(row_scaled_add_kernel<bf16>, dim3(grid_for(total)), dim3(256), 0, stream, dst, static_cast<const bf16*>(x), w, ldw, first, count, total, W);
+    sb::launch_pdl(row_scaled_add_kernel<bf16>, dim3(n), dim3(256), 0, stream, dst, static_cast<const bf16*>(x), w, ldw, first, count, W);
   else
     return sb::fail("sb_row_scaled_add: unsupported dtype %d", x_dtype);
   return sb::check_launch("sb_row_scaled_add");

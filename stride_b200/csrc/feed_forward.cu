@@ -133,21 +133,29 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ldz, cons
   }
 }
 
+// A block per row; the row's expert weights in shared memory first.
 template <class TO>
-__global__ void moe_activate_kernel(const float* __restrict__ up, int n_partials, int64_t partial_stride, const float* __restrict__ weights, int ldw,
-                                    TO* __restrict__ out, int64_t total, int EF, int F) {
+__global__ void __launch_bounds__(256) moe_activate_kernel(const float* __restrict__ up, int n_partials, int64_t partial_stride,
+                                                           const float* __restrict__ weights, int ldw, TO* __restrict__ out, int E, int F) {
+  __shared__ float g[256];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / EF;
-    const int e = static_cast<int>(i % EF) / F;
-    const float g = weights[r * ldw + e];
-    float v = 0.0f;
-    if (g != 0.0f) {
-      const float z = fmaxf(folded(up + i, n_partials, partial_stride), 0.0f);
-      v = g * (z * z);
+  const int64_t r = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) g[e] = weights[r * ldw + e];
+  __syncthreads();
+  const int EF = E * F;
+  const float* src = up + r * EF;
+  TO* dst = out + r * EF;
+  for (int e = 0; e < E; ++e) {
+    const float w = g[e];
+    if (w == 0.0f) {
+      for (int j = threadIdx.x; j < F; j += blockDim.x) dst[e * F + j] = sb::narrow<TO>(0.0f);
+    } else {
+      for (int j = threadIdx.x; j < F; j += blockDim.x) {
+        const float z = fmaxf(folded(src + e * F + j, n_partials, partial_stride), 0.0f);
+        dst[e * F + j] = sb::narrow<TO>(w * (z * z));
+      }
     }
-    out[i] = sb::narrow<TO>(v);
   }
 }
 
@@ -192,13 +200,11 @@ SB_EXPORT int sb_moe_activate(const float* up, int n_partials, int64_t partial_s
                               int n, int E, int F, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n_partials < 1 || E <= 0 || F <= 0) return sb::fail("sb_moe_activate: n_partials %d, %d experts of %d", n_partials, E, F);
-  const int64_t total = static_cast<int64_t>(n) * E * F;
-  const int64_t blocks = (total + 255) / 256, most = static_cast<int64_t>(sb::sm_count()) * 16;
-  const int grid = static_cast<int>(blocks < most ? blocks : most);
+  if (E > 256) return sb::fail("sb_moe_activate: %d experts (at most 256)", E);
   if (out_dtype == 0)
-    sb::launch_pdl(moe_activate_kernel<float>, dim3(grid), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<float*>(out), total, E * F, F);
+    sb::launch_pdl(moe_activate_kernel<float>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<float*>(out), E, F);
   else if (out_dtype == 1)
-    sb::launch_pdl(moe_activate_kernel<bf16>, dim3(grid), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<bf16*>(out), total, E * F, F);
+    sb::launch_pdl(moe_activate_kernel<bf16>, dim3(n), dim3(256), 0, stream, up, n_partials, partial_stride, weights, ldw, static_cast<bf16*>(out), E, F);
   else
     return sb::fail("sb_moe_activate: unsupported output dtype %d", out_dtype);
   return sb::check_launch("sb_moe_activate");

@@ -77,41 +77,74 @@ struct ScanParams {
   int H, D, V;
 };
 
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+
+// The q, g, k rows and the CTA's 32 value columns of a chunk of kChunk tokens reach shared memory by asynchronous copies, a chunk
+// ahead of the one being walked (two staging buffers). VEC = 4: every size and offset is a multiple of four floats, 16 bytes a copy.
+template <int VEC>
 __global__ void __launch_bounds__(512) gated_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(16) float smem[];
   sb::grid_launch_dependents();
   const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
   const int parts = blockDim.x >> 5, Dp = parts * R;
   const int part = threadIdx.x >> 5, cl = threadIdx.x & 31;
-  float* sq = smem;                    // [kChunk][Dp]
-  float* sg = sq + kChunk * Dp;
-  float* sk = sg + kChunk * Dp;
-  float* sv = sk + kChunk * Dp;        // [kChunk][32]
-  float* so = sv + kChunk * 32;        // [parts][kChunk][32]
+  const int stage = kChunk * (3 * Dp + 32);       // floats of a staging buffer: q, g, k [kChunk][Dp], v [kChunk][32]
+  float* so = smem + 2 * stage;                    // [parts][kChunk][32]
   const int slot = p.meta[e], row0 = p.meta[p.meta_stride + e], len = p.meta[2 * p.meta_stride + e], pos0 = p.meta[3 * p.meta_stride + e];
   const bool live = c0 + cl < p.V;
+  const int vn = min(32, p.V - c0);
   const int dn = min(R, p.D - part * R);
   float* st = p.state + ((static_cast<int64_t>(slot) * p.H + h) * p.D + part * R) * p.V + c0 + cl;
+  // nothing copies into the cells beyond D and beyond the CTA's existing columns: they are zero for good
+  if (Dp != p.D || vn != 32)
+    for (int i = threadIdx.x; i < 2 * stage; i += blockDim.x) smem[i] = 0.0f;
   sb::grid_dependency_wait();
+  __syncthreads();
   float S[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) S[i] = (pos0 > 0 && live && i < dn) ? st[static_cast<int64_t>(i) * p.V] : 0.0f;
-  for (int t0 = 0; t0 < len; t0 += kChunk) {
-    const int nt = min(kChunk, len - t0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * Dp; idx += blockDim.x) {
-      const int t = idx / Dp, d = idx % Dp;
-      const float* src = p.act + static_cast<int64_t>(row0 + t0 + t) * p.width + h * p.D + d;
-      const bool in = d < p.D;
-      sq[idx] = in ? src[p.q_off] : 0.0f;
-      sg[idx] = in ? src[p.g_off] : 0.0f;
-      sk[idx] = in ? src[p.k_off] : 0.0f;
+  const int du = p.D / VEC, vu = vn / VEC, per_token = 3 * du + vu;
+  auto request = [&](int chunk) {
+    float* sq = smem + (chunk & 1) * stage;
+    const int nt = min(kChunk, len - chunk * kChunk);
+    for (int i = threadIdx.x; i < nt * per_token; i += blockDim.x) {
+      const int t = i / per_token, j = i % per_token;
+      const float* src = p.act + static_cast<int64_t>(row0 + chunk * kChunk + t) * p.width;
+      float* dst;
+      if (j < 3 * du) {
+        const int which = j / du, u = j % du;
+        src += (which == 0 ? p.q_off : which == 1 ? p.g_off : p.k_off) + h * p.D + u * VEC;
+        dst = sq + which * kChunk * Dp + t * Dp + u * VEC;
+      } else {
+        const int u = j - 3 * du;
+        src += p.v_off + h * p.V + c0 + u * VEC;
+        dst = sq + 3 * kChunk * Dp + t * 32 + u * VEC;
+      }
+      if (VEC == 4) copy_async16(dst, src);
+      else copy_async4(dst, src);
     }
-    for (int idx = threadIdx.x; idx < nt * 32; idx += blockDim.x) {
-      const int t = idx >> 5, c = idx & 31;
-      sv[idx] = c0 + c < p.V ? p.act[static_cast<int64_t>(row0 + t0 + t) * p.width + p.v_off + h * p.V + c0 + c] : 0.0f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int chunks = (len + kChunk - 1) / kChunk;
+  request(0);
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    if (chunk + 1 < chunks) {
+      request(chunk + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const int nt = min(kChunk, len - chunk * kChunk);
+    const float* sq = smem + (chunk & 1) * stage;
+    const float* sg = sq + kChunk * Dp;
+    const float* sk = sg + kChunk * Dp;
+    const float* sv = sk + kChunk * Dp;
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + part * R);
       const float4* g4 = reinterpret_cast<const float4*>(sg + t * Dp + part * R);
@@ -138,7 +171,7 @@ __global__ void __launch_bounds__(512) gated_scan_kernel(const ScanParams p) {
       if (c0 + c < p.V) {
         float sum = so[t * 32 + c];
         for (int q = 1; q < parts; ++q) sum += so[(q * kChunk + t) * 32 + c];
-        p.out[static_cast<int64_t>(row0 + t0 + t) * p.H * p.V + h * p.V + c0 + c] = sum;
+        p.out[static_cast<int64_t>(row0 + chunk * kChunk + t) * p.H * p.V + h * p.V + c0 + c] = sum;
       }
     }
   }
@@ -194,12 +227,18 @@ SB_EXPORT int sb_gated_scan(const float* act, int width, int q_off, int g_off, i
   if (H <= 0 || D <= 0 || V <= 0 || D > 256) return sb::fail("sb_gated_scan: heads %d, key size %d (at most 256), value size %d", H, D, V);
   const int parts = (D + R - 1) / R, Dp = parts * R;
   ScanParams p{act, width, q_off, g_off, k_off, v_off, meta, meta_stride, state, out, H, D, V};
-  const size_t smem = sizeof(float) * (static_cast<size_t>(3) * kChunk * Dp + kChunk * 32 + static_cast<size_t>(parts) * kChunk * 32);
-  if (smem > 48 * 1024) {
-    if (smem > 200 * 1024) return sb::fail("sb_gated_scan: key size %d does not fit shared memory", D);
-    cudaFuncSetAttribute(gated_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = sizeof(float) * (static_cast<size_t>(2) * kChunk * (3 * Dp + 32) + static_cast<size_t>(parts) * kChunk * 32);
+  if (smem > 200 * 1024) return sb::fail("sb_gated_scan: key size %d does not fit shared memory", D);
+  const bool vec = D % 4 == 0 && V % 4 == 0 && width % 4 == 0 && q_off % 4 == 0 && g_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(act) & 15) == 0;
+  static sb::DeviceOnce once;
+  if (once.needed()) {
+    cudaFuncSetAttribute(gated_scan_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gated_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    once.done();
   }
-  sb::launch_pdl(gated_scan_kernel, dim3(entries, H, (V + 31) / 32), dim3(parts * 32), smem, stream, p);
+  if (vec) sb::launch_pdl(gated_scan_kernel<4>, dim3(entries, H, (V + 31) / 32), dim3(parts * 32), smem, stream, p);
+  else sb::launch_pdl(gated_scan_kernel<1>, dim3(entries, H, (V + 31) / 32), dim3(parts * 32), smem, stream, p);
   return sb::check_launch("sb_gated_scan");
 }
 

@@ -159,6 +159,206 @@ __global__ void __launch_bounds__(kWarps * 32) sigmoid_attention_kernel(AttnPara
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// The bfloat16 form on the tensor cores (mma.sync.m16n8k16, float32 accumulation). A CTA of four warps owns 64 rows of one
+// key/value head: the 64 / Hg consecutive positions of one entry times the Hg query heads of the group, 16 rows a warp. It walks
+// the tiles of 64 keys (cut by ABSOLUTE position) that any of its rows sees, in ascending order: S = Q K^T, the weights
+// sigmoid(scale S + bias) in 32-bit with 0 for keys a row does not see, each weight split into two bfloat16 parts hi + lo
+// (|w - hi - lo| <= 2^-17 w), O += hi V + lo V. A key that a row does not see adds exact zeros, so a row's result depends on its
+// own position alone: a token has the same bits in a prompt, in a portion and decoded alone (where 64 / Hg - 1 positions of the
+// tile are empty; the step is bound by the keys' and values' bytes then, not by the products).
+// Needs key sizes that are a multiple of 16 up to 256, value sizes that are a multiple of 16 up to 128 and a power of two up to 16 of
+// query heads a key head; everything else takes sigmoid_attention_kernel.
+constexpr int kTile = 64;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void copy16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+
+struct TileParams {
+  const bf16* q;             // [n][H D]
+  bf16* out;                 // [n][H Dv]
+  const bf16* pages;
+  const int32_t* block_table;
+  int max_pages, page_size;
+  int64_t page_stride, v_offset, head_stride;
+  const int32_t* meta;       // [4][meta_stride]: slot, first row, length, first position of every entry
+  int meta_stride, entries;
+  const float* bias;
+  int H, G, D, Dv, Dc;
+  int window;
+  float scale;
+};
+
+template <int NV>   // value size / 16
+__global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_kernel(TileParams p) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  sb::grid_launch_dependents();
+  const int Hg = p.H / p.G, PT = kTile / Hg, g = blockIdx.y;
+  const int ldk = p.D + 8, ldv = p.Dv + 8;                      // padded rows: ldmatrix without bank conflicts
+  bf16* Qs = reinterpret_cast<bf16*>(raw);                      // [64][ldk]
+  bf16* stage0 = Qs + kTile * ldk;                              // two staging buffers of keys [64][ldk] and values [64][ldv]
+  const int stage_elems = kTile * (ldk + ldv);
+  // which entry and which tile of its positions this CTA is
+  int e = 0, tile = blockIdx.x, len = 0;
+  for (; e < p.entries; ++e) {
+    len = p.meta[2 * p.meta_stride + e];
+    const int tiles = (len + PT - 1) / PT;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (e >= p.entries) return;
+  const int slot = p.meta[e], row0 = p.meta[p.meta_stride + e], pos0 = p.meta[3 * p.meta_stride + e];
+  const int t0 = tile * PT, nt = min(PT, len - t0);            // positions pos0 + t0 .. + nt - 1
+  const int first_pos = pos0 + t0, last_pos = first_pos + nt - 1;
+  const int first_key = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  sb::grid_dependency_wait();
+  // Q: row r = (position t0 + r / Hg, head g Hg + r % Hg); rows beyond the entry are zero
+  const int dchunks = p.D / 8;
+  for (int i = threadIdx.x; i < kTile * dchunks; i += blockDim.x) {
+    const int r = i / dchunks, c = i % dchunks, t = r / Hg;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < nt) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(row0 + t0 + t) * p.H + g * Hg + r % Hg) * p.D + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * ldk + c * 8) = v;
+  }
+  // (A warp none of whose 16 rows exists, as with a decoded token, which fills the first Hg rows of the tile only, multiplies all the
+  // same: leaving it out made the step slower, 0.196 against 0.128 ms for 64 decoded tokens over 1,024 keys, since the one warp with rows
+  // then is what every barrier of the CTA waits for.)
+  constexpr bool active = true;
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int p_lo = r_lo / Hg < nt ? first_pos + r_lo / Hg : -1, p_hi = r_hi / Hg < nt ? first_pos + r_hi / Hg : -1;
+  const float b_lo = p.bias != nullptr ? p.bias[g * Hg + r_lo % Hg] : 0.0f, b_hi = p.bias != nullptr ? p.bias[g * Hg + r_hi % Hg] : 0.0f;
+  float o[2 * NV][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  const bf16* base = p.pages + static_cast<int64_t>(g) * p.head_stride;
+  const int vchunks = p.Dv / 8;
+  // a tile's keys and values are requested (asynchronous copies) while the tile before is multiplied
+  auto request = [&](int kt, int buf) {
+    bf16* Ks = stage0 + buf * stage_elems;
+    bf16* Vs = Ks + kTile * ldk;
+    for (int i = threadIdx.x; i < kTile * (dchunks + vchunks); i += blockDim.x) {
+      const int r = i / (dchunks + vchunks), c = i % (dchunks + vchunks), j = kt * kTile + r;
+      const bool is_v = c >= dchunks;
+      bf16* dst = is_v ? Vs + r * ldv + (c - dchunks) * 8 : Ks + r * ldk + c * 8;
+      if (j >= first_key && j <= last_pos) {
+        const bf16* src = base + static_cast<int64_t>(table[j / p.page_size]) * p.page_stride + static_cast<int64_t>(j % p.page_size) * p.Dc +
+                          (is_v ? p.v_offset + (c - dchunks) * 8 : c * 8);
+        copy16(dst, src);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int kt_first = first_key / kTile, kt_last = last_pos / kTile;
+  request(kt_first, 0);
+  for (int kt = kt_first; kt <= kt_last; ++kt) {
+    const int buf = (kt - kt_first) & 1;
+    if (kt < kt_last) {
+      request(kt + 1, buf ^ 1);           // (the buffer of tile kt - 1: every warp left it before the barrier at the end of that tile)
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* Ks = stage0 + buf * stage_elems;
+    const bf16* Vs = Ks + kTile * ldk;
+    if (active) {
+    // S = Q K^T for this warp's 16 rows and the tile's 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int k0 = 0; k0 < p.D; k0 += 16) {
+      uint32_t a[4];
+      ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * ldk + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {                             // two n8 tiles of keys at a time
+        uint32_t b[4];
+        ldmatrix_x4(b, Ks + (n * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * n], a, b[0], b[1]);
+        mma_bf16(s[2 * n + 1], a, b[2], b[3]);
+      }
+    }
+    // the weights, split in two bfloat16 parts, as A operands of the value product
+    uint32_t hi[4][4], lo[4][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      float w[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = kt * kTile + n * 8 + (lane & 3) * 2 + (c & 1);
+        const int pos = c < 2 ? p_lo : p_hi;
+        const bool seen = j <= pos && (p.window <= 0 || pos - j < p.window);
+        const float x = fmaf(s[n][c], p.scale, c < 2 ? b_lo : b_hi);
+        w[c] = seen ? __fdividef(1.0f, 1.0f + __expf(-x)) : 0.0f;
+      }
+      const __nv_bfloat162 h01 = __floats2bfloat162_rn(w[0], w[1]), h23 = __floats2bfloat162_rn(w[2], w[3]);
+      const int kk = n >> 1, half = (n & 1) * 2;                // tile n is columns 8 (n & 1) .. of k step n / 2
+      hi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+      hi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+      lo[kk][half] = pack_bf16(w[0] - __low2float(h01), w[1] - __high2float(h01));
+      lo[kk][half + 1] = pack_bf16(w[2] - __low2float(h23), w[3] - __high2float(h23));
+    }
+    // O += hi V + lo V
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int nv = 0; nv < NV; ++nv) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + nv * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * nv], hi[kk], b[0], b[1]);
+        mma_bf16(o[2 * nv], lo[kk], b[0], b[1]);
+        mma_bf16(o[2 * nv + 1], hi[kk], b[2], b[3]);
+        mma_bf16(o[2 * nv + 1], lo[kk], b[2], b[3]);
+      }
+    }
+    }
+    __syncthreads();                      // this tile's buffer may be written again
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r_hi : r_lo;
+    if (r / Hg >= nt) continue;
+    bf16* dst = p.out + (static_cast<int64_t>(row0 + t0 + r / Hg) * p.H + g * Hg + r % Hg) * p.Dv + (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i)
+      *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * half], o[i][2 * half + 1]);
+  }
+}
+
+template <int NV>
+int launch_tiles(const TileParams& p, int n, cudaStream_t stream) {
+  const int Hg = p.H / p.G, PT = kTile / Hg;
+  const size_t smem = sizeof(bf16) * kTile * (3 * (p.D + 8) + 2 * (p.Dv + 8));
+  static sb::DeviceOnce once;
+  if (once.needed()) {
+    cudaFuncSetAttribute(sigmoid_attention_tile_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    once.done();
+  }
+  sb::launch_pdl(sigmoid_attention_tile_kernel<NV>, dim3((n + PT - 1) / PT + p.entries, p.G), dim3(128), smem, stream, p);
+  return sb::check_launch("sb_sigmoid_attention_tiles");
+}
+
 }  // namespace
 
 SB_EXPORT int sb_qkv_rotate_append(const float* qkv, int n_partials, int64_t partial_stride, const int32_t* positions, const int32_t* slots,
@@ -217,4 +417,42 @@ SB_EXPORT int sb_op_sigmoid_attention(const SbOp* op, const SbStep* s, void* str
                               (int)op->i[5], (int)op->i[6], op->i[7], op->i[8], op->i[9], positions(s), slots(s), ptr<const float>(op->i[10]), s->n,
                               (int)op->i[11], (int)op->i[12], (int)op->i[13], (int)op->i[14], (int)op->i[15], (int)op->i[16], (float)op->f[0],
                               static_cast<cudaStream_t>(stream));
+}
+
+// The tensor-core form: whether it takes a shape, and the launch. Entries come from the step's records on the device (meta).
+SB_EXPORT int sb_sigmoid_attention_tiles_supported(int H, int G, int D, int Dv, int Dc) {
+  if (G <= 0 || H % G != 0) return 0;
+  const int Hg = H / G;
+  return Hg <= 16 && (Hg & (Hg - 1)) == 0 && D % 16 == 0 && D >= 16 && D <= 256 && Dv % 16 == 0 && Dv >= 16 && Dv <= 128 && Dc % 8 == 0;
+}
+
+SB_EXPORT int sb_sigmoid_attention_tiles(const void* q, void* out, const void* pages, const int32_t* block_table, int max_pages, int page_size,
+                                         int64_t page_stride, int64_t v_offset, int64_t head_stride, const int32_t* meta, int meta_stride, int entries,
+                                         const float* bias, int n, int H, int G, int D, int Dv, int Dc, int window, float scale, cudaStream_t stream) {
+  if (n <= 0 || entries <= 0) return 0;
+  if (!sb_sigmoid_attention_tiles_supported(H, G, D, Dv, Dc))
+    return sb::fail("sb_sigmoid_attention_tiles: heads %d / %d, key size %d, value size %d are not a shape of the tensor-core form", H, G, D, Dv);
+  TileParams p{static_cast<const bf16*>(q), static_cast<bf16*>(out), static_cast<const bf16*>(pages), block_table, max_pages, page_size, page_stride,
+               v_offset, head_stride, meta, meta_stride, entries, bias, H, G, D, Dv, Dc, window, scale};
+  switch (Dv / 16) {
+    case 1: return launch_tiles<1>(p, n, stream);
+    case 2: return launch_tiles<2>(p, n, stream);
+    case 3: return launch_tiles<3>(p, n, stream);
+    case 4: return launch_tiles<4>(p, n, stream);
+    case 5: return launch_tiles<5>(p, n, stream);
+    case 6: return launch_tiles<6>(p, n, stream);
+    case 7: return launch_tiles<7>(p, n, stream);
+    default: return launch_tiles<8>(p, n, stream);
+  }
+}
+
+// i: 0 q, 1 out, 2 pages, 3 block table, 4 max_pages, 5 page_size, 6 page_stride, 7 v_offset, 8 head_stride, 9 bias, 10 H, 11 G, 12 D, 13 Dv,
+//    14 Dc, 15 window      f: 0 scale
+SB_EXPORT int sb_op_sigmoid_attention_tiles(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->n <= 0) return SB_OP_SKIPPED;
+  return sb_sigmoid_attention_tiles(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), ptr<const int32_t>(op->i[3]), (int)op->i[4],
+                                    (int)op->i[5], op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, s->entries, ptr<const float>(op->i[9]), s->n,
+                                    (int)op->i[10], (int)op->i[11], (int)op->i[12], (int)op->i[13], (int)op->i[14], (int)op->i[15], (float)op->f[0],
+                                    static_cast<cudaStream_t>(stream));
 }

@@ -147,7 +147,7 @@ class StepProgram:
         self.workspace = workspace
         self.max_rows = max_rows
         self.few_tokens = few_tokens          # up to this many tokens a projection leaves one buffer per K range
-        self.h = None                         # the residual stream [max_rows, hidden] float32
+        self._h, self.h_touched = None, False # the residual stream [max_rows, hidden] float32 (`h`), and whether it was asked for since it was set
         self.embedding_output = None          # the embedding's rows [max_rows, hidden] float32, when a part reads them again
         self.pending = None                   # (flat buffer, K ranges, width) left by the last projection, or None
         self._libraries: list = []            # per operation: the library its function lives in (for its error text)
@@ -163,6 +163,17 @@ class StepProgram:
         handle, self._handle = getattr(self, "_handle", None), None
         if handle:
             self._lib.sb_program_destroy(handle)
+
+    @property
+    def h(self):
+        """The buffer that operations adding to the stream write into. A block that runs a sublayer on a branch puts the branch's
+        buffer here meanwhile, and learns from `h_touched` whether any operation wrote into it (or only left partial sums pending)."""
+        self.h_touched = True
+        return self._h
+
+    @h.setter
+    def h(self, buffer):
+        self._h, self.h_touched = buffer, False
 
     def __len__(self):
         return self._lib.sb_program_size(self._handle)

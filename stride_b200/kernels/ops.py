@@ -496,6 +496,28 @@ def sigmoid_attention(q, out, cache_layer, block_table, positions, slots, bias, 
                    num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4], window, scale, _stream()))
 
 
+def sigmoid_attention_tiles_supported(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, row: int) -> bool:
+    """True if the tensor-core form of the sigmoid attention takes this shape (bfloat16 only)."""
+    lib = library("sigmoid_attention")
+    lib.sb_sigmoid_attention_tiles_supported.argtypes = [c_int] * 5
+    lib.sb_sigmoid_attention_tiles_supported.restype = c_int
+    return bool(lib.sb_sigmoid_attention_tiles_supported(num_heads, num_kv_heads, key_dim, value_dim, row))
+
+
+def sigmoid_attention_tiles(q, out, cache_layer, block_table, entry_meta, entries: int, bias, num_heads: int, num_kv_heads: int, key_dim: int,
+                            value_dim: int, window: int, scale: float) -> None:
+    """`sigmoid_attention` on the tensor cores (bfloat16 q, out and cache), entry by entry of the step."""
+    _cuda(q, out, cache_layer, block_table, entry_meta, bias)
+    if not (q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16):
+        raise TypeError("sigmoid_attention_tiles takes bfloat16 q, out and cache")
+    lib, fn = _fn("sigmoid_attention", "sb_sigmoid_attention_tiles",
+                  [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), _ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0),
+                   cache_layer.stride(1), cache_layer.stride(2), _ptr(entry_meta), entry_meta.stride(0), entries, _ptr(bias), q.shape[0],
+                   num_heads, num_kv_heads, key_dim, value_dim, cache_layer.shape[4], window, scale, _stream()))
+
+
 def hgrn2_activate(proj: torch.Tensor, f_bias, lower, act: torch.Tensor, HD: int, HV: int) -> None:
     """act [n, 3 HD + HV] = q | g | k | v from the sums of proj [P, n, 2 HD + HV] = q | f | v: q = silu, g = lower + (1 - lower) sigmoid(f + bias),
     k = 1 - g, v as projected."""
@@ -536,16 +558,16 @@ def rglru_conv(proj: torch.Tensor, x_bias, taps, conv_bias, positions, slots, st
                    _ptr(u), n, C, taps.shape[1], _stream()))
 
 
-def rglru_gates(gates: torch.Tensor, r_bias, i_bias, lam, y_bias, u, proj, a, d, y, blocks: int) -> None:
-    """a = exp(-8 sigmoid(gates_r + r_bias) softplus(lam)), d = sqrt(1 - a^2) sigmoid(gates_i + i_bias) u, y = gelu_tanh(proj_y + y_bias);
-    gates [n, blocks, 2, C / blocks]."""
-    _cuda(gates, r_bias, i_bias, lam, y_bias, u, proj, a, d, y)
-    lib, fn = _fn("rglru", "sb_rglru_gates", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_void_p,
-                                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+def rglru_gates(gate_weights: torch.Tensor, r_bias, i_bias, lam, y_bias, u, proj, a, d, y) -> None:
+    """a = exp(-8 sigmoid(A_b u_b + r_bias) softplus(lam)), d = sqrt(1 - a^2) sigmoid(I_b u_b + i_bias) u, y = gelu_tanh(proj_y + y_bias);
+    gate_weights [blocks, bw, 2 bw]: per block of channels A_b and I_b side by side, transposed ([input, output])."""
+    _cuda(gate_weights, r_bias, i_bias, lam, y_bias, u, proj, a, d, y)
+    lib, fn = _fn("rglru", "sb_rglru_gates", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64,
+                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     p, P, stride = _partials(proj)
     n, C = u.shape
-    _check(lib, fn(_ptr(gates), _ptr(r_bias), _ptr(i_bias), _ptr(lam), _ptr(y_bias), dtype_code(lam.dtype), _ptr(u), p, P, stride, _ptr(a), _ptr(d),
-                   _ptr(y), n, C, blocks, _stream()))
+    _check(lib, fn(_ptr(gate_weights), dtype_code(gate_weights.dtype), _ptr(r_bias), _ptr(i_bias), _ptr(lam), _ptr(y_bias), dtype_code(lam.dtype),
+                   _ptr(u), p, P, stride, _ptr(a), _ptr(d), _ptr(y), n, C, gate_weights.shape[0], _stream()))
 
 
 def rglru_scan(a, d, y, proj, x_bias, entry_meta: torch.Tensor, entries: int, state: torch.Tensor, out: torch.Tensor, taps: int) -> None:

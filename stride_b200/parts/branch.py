@@ -5,7 +5,8 @@ sublayer's result. Blocks "prenorm_scaled" and "prenorm_scaled_mixer": h += w1 *
 h += w2 * feed_forward(norm(h)). The mixer and the feed-forward are the same parts that other blocks use: they are
 handed a branch, a `ResidualStream` over a float32 buffer that is zero between uses, instead of the stream, so their
 last projection adds into the branch or leaves its K ranges' partial sums pending on it; the scale then takes
-both into the stream in one pass (csrc/branch.cu) and leaves the branch zero again."""
+both into the stream in one pass (csrc/branch.cu) and leaves the branch zero again. A part that is several parts side by
+side may hand its members' branches over unfolded (`forward_sources` / `emit_sources`), so that one pass scales and adds them all."""
 from __future__ import annotations
 
 import torch
@@ -16,14 +17,32 @@ from .context import ResidualStream
 from .spec import TensorPlan
 
 
+class Branch(ResidualStream):
+    """A residual stream over a branch buffer that notes whether anything asked for the buffer: a sublayer whose last projection
+    only leaves partial sums pending never does, and the fold then neither reads nor clears the buffer."""
+
+    def __init__(self, buffer: torch.Tensor):
+        self._buffer, self.pending, self.touched = buffer, None, False
+
+    @property
+    def h(self):
+        self.touched = True
+        return self._buffer
+
+    def source(self):
+        """(buffer or None, pending partial sums or None), what a fold takes."""
+        return (self._buffer if self.touched else None), self.take_pending()
+
+
 def emit_on_branch(program, branch: torch.Tensor, emit) -> tuple:
-    """Run `emit()` (a part's `emit` that adds to the program's stream) with `branch` in the stream's place; returns the
-    partial sums it left pending, or None."""
+    """Run `emit()` (a part's `emit` that adds to the program's stream) with `branch` in the stream's place; returns (the branch if an
+    operation wrote into it, else None; the partial sums left pending, or None)."""
     program.need_folded("a sublayer on a branch")
-    main, program.h = program.h, branch
+    main = program._h
+    program.h = branch
     try:
         emit()
-        return program.take_pending()
+        return (branch if program.h_touched else None), program.take_pending()
     finally:
         program.h = main
 
@@ -50,15 +69,29 @@ class LayerScale(BranchScale):
     def kernel_libraries(self):
         return {"branch"}
 
-    def forward(self, ctx, branch, stream):
+    def forward(self, ctx, sources, stream):
+        """sources: one or two (Branch, constant)."""
         stream.fold()
-        ops.branch_fold(stream.h, a=branch.h, a_partials=branch.take_pending(), gain=self.weight)
+        (a, pa), ca = sources[0][0].source(), sources[0][1]
+        (b, pb), cb = (sources[1][0].source(), sources[1][1]) if len(sources) > 1 else ((None, None), 1.0)
+        ops.branch_fold(stream.h, a=a, a_partials=pa, ca=ca, b=b, b_partials=pb, cb=cb, gain=self.weight)
 
-    def emit(self, program, branch, pending):
-        flat, S, _ = pending or (None, 1, 0)
+    def emit(self, program, sources):
+        """sources: one or two (buffer or None, pending partial sums or None, constant)."""
         program.need_folded("a layer scale")
-        program.add("branch", "sb_op_branch_fold", [program.h, branch, flat, S, program.few_tokens, None, None, 1, self.weight, self.weight.dtype,
-                                                    self.size], [1.0, 1.0])
+        emit_fold(program, sources, self.weight, self.size)
+
+
+def emit_fold(program, sources, gain, width: int) -> None:
+    """The operation that takes one or two branches (buffer or None, pending or None, constant) into the program's stream."""
+    if not 1 <= len(sources) <= 2:
+        raise ValueError("a fold takes one or two branches")
+    (a, pa, ca), (b, pb, cb) = sources[0], sources[1] if len(sources) > 1 else (None, None, 1.0)
+    (fa, Sa, _), (fb, Sb, _) = pa or (None, 1, 0), pb or (None, 1, 0)
+    if a is None and fa is None:
+        raise ValueError("a branch that nothing wrote into")
+    program.add("branch", "sb_op_branch_fold", [program.h, a, fa, Sa, program.few_tokens, b, fb, Sb, gain, gain.dtype if gain is not None else 0, width],
+                [ca, cb])
 
 
 class _ScaledBlock(Block):
@@ -67,21 +100,30 @@ class _ScaledBlock(Block):
     def _branch(self, ws, rows, width):
         return ws.get("block.branch", rows, (width,), torch.float32)
 
-    def _sublayer(self, ctx, stream, norm, run, scale):
+    def _sublayer(self, ctx, stream, norm, part, run, scale):
+        """`part` may offer `forward_sources(ctx, x, ...)`: its result as branches with constants that it leaves to the caller to
+        fold (several mixers side by side do); every other part runs on one branch."""
         width = stream.h.shape[1]
         x = ctx.workspace.get("block.x", ctx.n, (width,), ctx.act_dtype)
-        branch = ResidualStream(self._branch(ctx.workspace, ctx.n, width))
         norm.forward(ctx, stream, x)
-        run(x, branch)
-        scale.forward(ctx, branch, stream)
+        if hasattr(part, "forward_sources"):
+            sources = run(part.forward_sources, x)
+        else:
+            branch = Branch(self._branch(ctx.workspace, ctx.n, width))
+            run(part.forward, x, branch)
+            sources = [(branch, 1.0)]
+        scale.forward(ctx, sources, stream)
 
-    def _emit_sublayer(self, program, norm, run, scale):
+    def _emit_sublayer(self, program, norm, part, run, scale):
         ws, width = program.workspace, program.h.shape[1]
         x = ws.get("block.x", ws.max_tokens, (width,), self.env.act_dtype)
-        branch = self._branch(ws, ws.max_tokens, width)
         norm.emit(program, x)
-        pending = emit_on_branch(program, branch, lambda: run(x))
-        scale.emit(program, branch, pending)
+        if hasattr(part, "emit_sources"):
+            sources = run(part.emit_sources, x)
+        else:
+            branch = self._branch(ws, ws.max_tokens, width)
+            sources = [(*emit_on_branch(program, branch, lambda: run(part.emit, x)), 1.0)]
+        scale.emit(program, sources)
 
 
 @register_part("block", "prenorm_scaled")
@@ -90,12 +132,12 @@ class PreNormScaledBlock(_ScaledBlock):
              "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_scale": "branch_scale"}
 
     def forward(self, ctx, stream, cache):
-        self._sublayer(ctx, stream, self.mixer_norm, lambda x, b: self.mixer.forward(ctx, x, b, cache), self.mixer_scale)
-        self._sublayer(ctx, stream, self.feed_forward_norm, lambda x, b: self.feed_forward.forward(ctx, x, b), self.feed_forward_scale)
+        self._sublayer(ctx, stream, self.mixer_norm, self.mixer, lambda f, x, *b: f(ctx, x, *b, cache), self.mixer_scale)
+        self._sublayer(ctx, stream, self.feed_forward_norm, self.feed_forward, lambda f, x, *b: f(ctx, x, *b), self.feed_forward_scale)
 
     def emit(self, program, cache):
-        self._emit_sublayer(program, self.mixer_norm, lambda x: self.mixer.emit(program, x, cache), self.mixer_scale)
-        self._emit_sublayer(program, self.feed_forward_norm, lambda x: self.feed_forward.emit(program, x), self.feed_forward_scale)
+        self._emit_sublayer(program, self.mixer_norm, self.mixer, lambda f, x: f(program, x, cache), self.mixer_scale)
+        self._emit_sublayer(program, self.feed_forward_norm, self.feed_forward, lambda f, x: f(program, x), self.feed_forward_scale)
 
 
 @register_part("block", "prenorm_scaled_mixer")
@@ -104,7 +146,7 @@ class PreNormScaledMixerBlock(_ScaledBlock):
     ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_scale": "branch_scale"}
 
     def forward(self, ctx, stream, cache):
-        self._sublayer(ctx, stream, self.mixer_norm, lambda x, b: self.mixer.forward(ctx, x, b, cache), self.mixer_scale)
+        self._sublayer(ctx, stream, self.mixer_norm, self.mixer, lambda f, x, *b: f(ctx, x, *b, cache), self.mixer_scale)
 
     def emit(self, program, cache):
-        self._emit_sublayer(program, self.mixer_norm, lambda x: self.mixer.emit(program, x, cache), self.mixer_scale)
+        self._emit_sublayer(program, self.mixer_norm, self.mixer, lambda f, x: f(program, x, cache), self.mixer_scale)

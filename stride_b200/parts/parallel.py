@@ -7,8 +7,7 @@ import torch
 
 from ..kernels import ops
 from .base import Mixer, part_class, register_part
-from .branch import emit_on_branch
-from .context import ResidualStream
+from .branch import Branch, emit_fold, emit_on_branch
 
 
 @register_part("mixer", "parallel")
@@ -48,17 +47,23 @@ class ParallelMixer(Mixer):
     def _buffers(self, ws, rows):
         return [ws.get(f"parallel.branch{k}", rows, (self.hidden,), torch.float32) for k in range(2)]
 
-    def forward(self, ctx, x, stream, cache):
-        branches = [ResidualStream(b) for b in self._buffers(ctx.workspace, ctx.n)]
+    def forward_sources(self, ctx, x, cache):
+        """The members' results as [(Branch, constant)], left to the caller to fold."""
+        branches = [Branch(b) for b in self._buffers(ctx.workspace, ctx.n)]
         for m, b, c in zip(self.members, branches, cache.parts):
             m.forward(ctx, x, b, c)
+        return list(zip(branches, self.scales))
+
+    def forward(self, ctx, x, stream, cache):
+        (a, ca), (b, cb) = self.forward_sources(ctx, x, cache)
         stream.fold()
-        (a, ca), (b, cb) = zip(branches, self.scales)
-        ops.branch_fold(stream.h, a=a.h, a_partials=a.take_pending(), ca=ca, b=b.h, b_partials=b.take_pending(), cb=cb)
+        (ah, ap), (bh, bp) = a.source(), b.source()
+        ops.branch_fold(stream.h, a=ah, a_partials=ap, ca=ca, b=bh, b_partials=bp, cb=cb)
+
+    def emit_sources(self, program, x, cache):
+        buffers = self._buffers(program.workspace, program.workspace.max_tokens)
+        return [(*emit_on_branch(program, buf, lambda m=m, c=c: m.emit(program, x, c)), scale)
+                for m, buf, c, scale in zip(self.members, buffers, cache.parts, self.scales)]
 
     def emit(self, program, x, cache):
-        buffers = self._buffers(program.workspace, program.workspace.max_tokens)
-        pending = [emit_on_branch(program, buf, lambda m=m, c=c: m.emit(program, x, c)) for m, buf, c in zip(self.members, buffers, cache.parts)]
-        (fa, Sa, _), (fb, Sb, _) = [p or (None, 1, 0) for p in pending]
-        program.add("branch", "sb_op_branch_fold", [program.h, buffers[0], fa, Sa, program.few_tokens, buffers[1], fb, Sb, None, 0, self.hidden],
-                    self.scales)
+        emit_fold(program, self.emit_sources(program, x, cache), None, self.hidden)

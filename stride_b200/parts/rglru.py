@@ -5,8 +5,8 @@ channel over the last `taps` inputs. The channels are cut into `blocks` equal pa
 and i = sigmoid(I_b u_b + i_b) with square matrices A_b, I_b. Then a = exp(-8 r softplus(lam)),
 S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t from S = 0, and the result is W_o (S * y). Per request the state record
 [taps, width] float32 holds the convolution's last taps - 1 inputs and S. The two input projections are one matrix
-product; everything between them and W_o is 32-bit in both precisions of the engine: the gates' products are true
-float32 products per block (csrc/gemm_f32.cu), the rest is csrc/rglru.cu."""
+product; everything between them and W_o is 32-bit in both precisions of the engine, the gates' products per block
+included (csrc/rglru.cu)."""
 from __future__ import annotations
 
 import torch
@@ -55,8 +55,9 @@ class RGLRUMixer(Mixer):
         r, i = tensors[t["r"]], tensors[t["i"]]
         if r.dtype != i.dtype:
             r, i = r.to(torch.float32), i.to(torch.float32)
-        # per block one matrix [2 bw, bw]: the rows of A_b, then those of I_b
-        self.gate_weights = torch.cat([r, i], dim=1).contiguous()
+        # per block one matrix [bw, 2 bw]: A_b and I_b side by side, transposed, so that the kernel's threads (one per output) read
+        # consecutive weights
+        self.gate_weights = torch.cat([r, i], dim=1).transpose(1, 2).contiguous()
 
     def weight_bytes(self):
         return self.proj.weight_bytes() + self.o.weight_bytes() + self.gate_weights.numel() * self.gate_weights.element_size()
@@ -65,18 +66,15 @@ class RGLRUMixer(Mixer):
         return CacheNeed("state", state_shape=(self.taps, self.width), state_dtype=torch.float32)
 
     def kernel_libraries(self):
-        return {"rglru", "gemm_f32", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
+        return {"rglru", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
 
     def forward(self, ctx, x, stream, cache):
         n, ws, C, bw = ctx.n, ctx.workspace, self.width, self.bw
         proj = self.proj.forward_partials(x, ws.raw("rglru.proj", (self.proj.partial_elems(ws.max_tokens),), torch.float32))
         u = ws.get("rglru.u", n, (C,), torch.float32)
         ops.rglru_conv(proj, self.x_bias, self.conv, self.conv_bias, ctx.positions, ctx.slots, cache.state, u)
-        gates = ws.get("rglru.gates", n, (2 * C,), torch.float32)
-        for b in range(self.blocks):
-            ops.gemm_f32(u[:, b * bw:(b + 1) * bw], self.gate_weights[b], gates[:, 2 * b * bw:2 * (b + 1) * bw])
         a, d, y = (ws.get("rglru." + name, n, (C,), torch.float32) for name in ("a", "d", "y"))
-        ops.rglru_gates(gates, self.r_bias, self.i_bias, self.lam, self.y_bias, u, proj, a, d, y, self.blocks)
+        ops.rglru_gates(self.gate_weights, self.r_bias, self.i_bias, self.lam, self.y_bias, u, proj, a, d, y)
         out = ws.get("rglru.out", n, (C,), ctx.act_dtype)
         ops.rglru_scan(a, d, y, proj, self.x_bias, ctx.entry_meta, ctx.entry_meta.shape[1], cache.state, out, self.taps)
         self.o.forward_add(out, stream, ws.raw("rglru.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
@@ -88,13 +86,9 @@ class RGLRUMixer(Mixer):
         S = self.proj.emit_partials(program, x, proj)
         u = ws.get("rglru.u", T, (C,), f32)
         program.add("rglru", "sb_op_rglru_conv", [proj, S, program.few_tokens, self.x_bias, self.conv, self.conv_bias, f32, cache.state, u, C, self.taps])
-        gates = ws.get("rglru.gates", T, (2 * C,), f32)
-        for b in range(self.blocks):
-            w = self.gate_weights[b]
-            program.add("gemm_f32", "sb_op_linear_f32", [u[:, b * bw:], f32, C, w, w.dtype, bw, gates[:, 2 * b * bw:], 2 * C, 2 * bw, bw, 0, 0])
         a, d, y = (ws.get("rglru." + name, T, (C,), f32) for name in ("a", "d", "y"))
-        program.add("rglru", "sb_op_rglru_gates", [gates, self.r_bias, self.i_bias, self.lam, self.y_bias, f32, u, proj, S, program.few_tokens, a, d, y,
-                                                   C, self.blocks])
+        program.add("rglru", "sb_op_rglru_gates", [self.gate_weights, self.gate_weights.dtype, self.r_bias, self.i_bias, self.lam, self.y_bias, f32, u,
+                                                   proj, S, program.few_tokens, a, d, y, C, self.blocks])
         out = ws.get("rglru.out", T, (C,), self.env.act_dtype)
         program.add("rglru", "sb_op_rglru_scan", [a, d, y, proj, S, program.few_tokens, self.x_bias, f32, cache.state, out, out.dtype, C, self.taps])
         self.o.emit_add(program, out, ws.raw("rglru.o_partials", (self.o.partial_elems(T),), f32))

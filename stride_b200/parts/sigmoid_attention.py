@@ -75,6 +75,12 @@ class SigmoidAttentionMixer(Mixer):
     def kernel_libraries(self):
         return {"sigmoid_attention", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
 
+    def _tiles(self) -> bool:
+        """The bfloat16 engine takes the tensor-core kernel where the shape allows it (key and value sizes that are multiples of 16,
+        a power of two of query heads a key head), the float32 engine and every other shape the kernel with a block per token and head."""
+        return self.env.act_dtype == torch.bfloat16 and ops.sigmoid_attention_tiles_supported(self.num_heads, self.num_kv_heads, self.key_dim,
+                                                                                              self.value_dim, self.row)
+
     def forward(self, ctx, x, stream, cache):
         n, ws, H, G, D, V = ctx.n, ctx.workspace, self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
         qkv = self.qkv.forward_partials(x, ws.raw("sattn.qkv", (self.qkv.partial_elems(ws.max_tokens),), torch.float32))
@@ -82,7 +88,11 @@ class SigmoidAttentionMixer(Mixer):
         ops.qkv_rotate_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table, H, G, D, V,
                               write_kv=cache.writes)
         mixed = ws.get("sattn.out", n, (H * V,), ctx.act_dtype)
-        ops.sigmoid_attention(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots, self.bias, H, G, D, V, self.window, self.scale)
+        if self._tiles():
+            ops.sigmoid_attention_tiles(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, ctx.entry_meta.shape[1], self.bias, H, G, D, V,
+                                        self.window, self.scale)
+        else:
+            ops.sigmoid_attention(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots, self.bias, H, G, D, V, self.window, self.scale)
         self.o.forward_add(mixed, stream, ws.raw("sattn.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
 
     def emit(self, program, x, cache):
@@ -97,6 +107,10 @@ class SigmoidAttentionMixer(Mixer):
         program.add("sigmoid_attention", "sb_op_qkv_rotate_append",
                     [qkv, S, program.few_tokens, self._cos_sin, self._rotary, q, q.dtype, pages, pages.dtype, table, *where, H, G, D, V,
                      pages.shape[4], int(cache.writes)])
-        program.add("sigmoid_attention", "sb_op_sigmoid_attention",
-                    [q, mixed, q.dtype, pages, table, *where, self.bias, H, G, D, V, pages.shape[4], self.window], [self.scale])
+        if self._tiles():
+            program.add("sigmoid_attention", "sb_op_sigmoid_attention_tiles",
+                        [q, mixed, pages, table, *where, self.bias, H, G, D, V, pages.shape[4], self.window], [self.scale])
+        else:
+            program.add("sigmoid_attention", "sb_op_sigmoid_attention",
+                        [q, mixed, q.dtype, pages, table, *where, self.bias, H, G, D, V, pages.shape[4], self.window], [self.scale])
         self.o.emit_add(program, mixed, ws.raw("sattn.o_partials", (self.o.partial_elems(T),), torch.float32))

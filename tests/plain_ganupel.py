@@ -140,11 +140,16 @@ def polynorm_feed_forward(h, tensors, prefix, eps, rnd=None):
     return rounded(act, rnd) @ w(tensors, prefix + "down").T
 
 
-def routed_feed_forward(h, tensors, prefix, mlp, rnd=None):
+def routed_feed_forward(h, tensors, prefix, mlp, rnd=None, margins=None):
+    """`margins` (a list) receives, per token, by how much the last chosen expert's choice score leads the first one left out:
+    where that is smaller than what rounding moves a score by, another implementation may rightly choose otherwise."""
     r = mlp["router"]
     E, I, top = r["experts"], r.get("identity", 0), r["top"]
     s = torch.softmax(h @ w(tensors, prefix + "router").T, dim=-1)             # [T, E + I]
     choice = s + w(tensors, prefix + "correction")
+    if margins is not None and top < E + I:
+        best = torch.topk(choice, top + 1, dim=-1).values
+        margins.append(best[:, -2] - best[:, -1])
     chosen = torch.topk(choice, top, dim=-1).indices                            # [T, top]
     picked = torch.gather(s, 1, chosen)
     weight = picked / (picked.sum(-1, keepdim=True) + 1e-20) * r["scale"]
@@ -159,7 +164,7 @@ def routed_feed_forward(h, tensors, prefix, mlp, rnd=None):
     return out
 
 
-def layer(x, tensors, i, spec, eps, rnd=None):
+def layer(x, tensors, i, spec, eps, rnd=None, margins=None):
     p = f"l{i}."
     h = rounded(offset_rms_norm(x, w(tensors, p + "norm1"), eps), rnd)
     if spec["type"] == "parallel":
@@ -175,18 +180,19 @@ def layer(x, tensors, i, spec, eps, rnd=None):
         if mlp["kind"] == "dense":
             y = polynorm_feed_forward(h, tensors, p + "mlp.", eps, rnd)
         else:
-            y = routed_feed_forward(h, tensors, p + "mlp.", mlp, rnd)
+            y = routed_feed_forward(h, tensors, p + "mlp.", mlp, rnd, margins)
         x = x + y * w(tensors, p + "ls2")
     return x
 
 
-def forward(config, tensors, tokens, rnd=None, keep_layers=False):
-    """Logits [T, vocab] (float64) of one sequence; with keep_layers also the stream after every layer."""
+def forward(config, tensors, tokens, rnd=None, keep_layers=False, margins=None):
+    """Logits [T, vocab] (float64) of one sequence; with keep_layers also the stream after every layer; `margins`: see
+    routed_feed_forward (one entry per routed layer)."""
     eps = config["norm"]["eps"]
     x = w(tensors, "embed")[torch.as_tensor(tokens, dtype=torch.long)]
     streams = []
     for i, spec in enumerate(config["layers"]):
-        x = layer(x, tensors, i, spec, eps, rnd)
+        x = layer(x, tensors, i, spec, eps, rnd, margins)
         streams.append(x)
     logits = rounded(offset_rms_norm(x, w(tensors, "final.norm"), eps), rnd) @ w(tensors, "head").T
     return (logits, streams) if keep_layers else logits

@@ -176,6 +176,55 @@ def test_sigmoid_attention_kernels(H, G, D, V, window, rot, page):
         assert (got.double() - want).abs().max() <= 2e-5 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("H,G,D,V,window,page", [(8, 2, 64, 64, 100, 32), (4, 2, 32, 48, 24, 16), (2, 2, 96, 96, 72, 64), (16, 1, 16, 128, 0, 8),
+                                                 (3, 3, 256, 16, 200, 16)])
+def test_sigmoid_attention_on_the_tensor_cores(H, G, D, V, window, page):
+    """The bfloat16 tile kernel against the kernel with a block per token and head on the same pages (the weights' two bfloat16
+    parts keep them to 2^-17, so what differs is the order of the sums), against the sum in 64-bit, and a request cut into a
+    prompt, portions and single tokens in the same bits."""
+    from stride_b200.kernels import ops
+    assert ops.sigmoid_attention_tiles_supported(H, G, D, V, max(D, V))
+    g = torch.Generator().manual_seed(H * D + V)
+    n, row, scale = 300, max(D, V), 0.11
+    per = -(-n // page)
+    perm = torch.randperm(per + 2, generator=g)[:per].to(torch.int32)
+    table = perm.view(1, per).to(DEV)
+    k = (torch.randn(n, G, D, generator=g)).to(torch.bfloat16)
+    v = (torch.randn(n, G, V, generator=g)).to(torch.bfloat16)
+    q = (torch.randn(n, H, D, generator=g)).to(torch.bfloat16)
+    bias = torch.randn(H, generator=g)
+    pages = torch.zeros(per + 2, 2, G, page, row, dtype=torch.bfloat16)
+    for j in range(n):
+        pages[perm[j // page], 0, :, j % page, :D] = k[j]
+        pages[perm[j // page], 1, :, j % page, :V] = v[j]
+    pages = pages.to(DEV)
+    want = torch.zeros(n, H, V, dtype=F)
+    i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+    seen = (j <= i) & ((i - j < window) if window else (j <= i))
+    for h in range(H):
+        w = torch.sigmoid(q[:, h].double() @ k[:, h // (H // G)].double().T * scale + bias[h].double()) * seen
+        want[:, h] = w @ v[:, h // (H // G)].double()
+
+    def run(a, b, tiles):
+        pos = torch.arange(a, b, dtype=torch.int32, device=DEV)
+        slot = torch.zeros(b - a, dtype=torch.int32, device=DEV)
+        out = torch.empty(b - a, H * V, dtype=torch.bfloat16, device=DEV)
+        qd = q[a:b].reshape(b - a, H * D).to(DEV)
+        if tiles:
+            ops.sigmoid_attention_tiles(qd, out, pages, table, _meta([(0, 0, b - a, a)]), 1, bias.to(DEV), H, G, D, V, window, scale)
+        else:
+            ops.sigmoid_attention(qd, out, pages, table, pos, slot, bias.to(DEV), H, G, D, V, window, scale)
+        return out.cpu()
+
+    whole, simple = run(0, n, True), run(0, n, False)
+    tol = 2.0 ** -7 * float(want.abs().max())
+    assert (whole.double().view(n, H, V) - want).abs().max() <= tol
+    assert (whole.double() - simple.double()).abs().max() <= tol
+    cuts = [0, 70, 71, 73, 130, 131, 290, 291, 300]
+    parts = torch.cat([run(a, b, True) for a, b in zip(cuts, cuts[1:])])
+    assert torch.equal(parts, whole)
+
+
 @pytest.mark.parametrize("window", [9, 64, 65])
 def test_a_key_at_the_window_edge_shows(window):
     """A value of 10,000 among values of order one: just inside the window it dominates the last token's output, just outside it
@@ -273,7 +322,7 @@ def test_hgrn2_activation_and_group_norm_kernels():
         assert (y.cpu().double() - ref).abs().max() <= tol * float(ref.abs().max())
 
 
-@pytest.mark.parametrize("C,B,K", [(80, 5, 3), (64, 1, 2), (256, 4, 4), (60, 3, 5), (48, 2, 1)])
+@pytest.mark.parametrize("C,B,K", [(80, 5, 3), (64, 1, 2), (256, 4, 4), (60, 3, 5), (48, 2, 1), (600, 2, 4)])
 def test_rglru_kernels_across_steps(C, B, K):
     """The recurrent block between its projections, with requests cut into steps of 1, 2 and more tokens than taps, beside one
     another and in slots that hold another request's record: against the plain block (whose projections are identities here),
@@ -289,18 +338,16 @@ def test_rglru_kernels_across_steps(C, B, K):
     inputs = [torch.randn(n, 2 * C, generator=gen) for n in lengths]
     wants = [plain.rglru(h.double(), t, "p.", {"width": C, "blocks": B}) for h in inputs]
     dev = lambda name: t[name].float().contiguous().to(DEV)
-    gate_w = torch.cat([t["p.ra"], t["p.ri"]], 1).contiguous().to(DEV)
+    gate_w = torch.cat([t["p.ra"], t["p.ri"]], 1).transpose(1, 2).contiguous().to(DEV)       # per block [input, outputs of r | i]
 
     def step(entries, rows, state):
         n = rows.shape[0]
         pos, slot = _rows(entries)
         proj = torch.stack([rows * 0.25, rows * 0.75]).to(DEV)
-        u, gates = torch.empty(n, C, device=DEV), torch.empty(n, 2 * C, device=DEV)
+        u = torch.empty(n, C, device=DEV)
         ops.rglru_conv(proj, dev("p.x.b"), dev("p.conv"), dev("p.conv.b"), pos, slot, state, u)
-        for b in range(B):
-            ops.gemm_f32(u[:, b * bw:(b + 1) * bw], gate_w[b], gates[:, 2 * b * bw:2 * (b + 1) * bw])
         a, d, y = (torch.empty(n, C, device=DEV) for _ in range(3))
-        ops.rglru_gates(gates, dev("p.ra.b").reshape(-1), dev("p.ri.b").reshape(-1), dev("p.lam"), dev("p.y.b"), u, proj, a, d, y, B)
+        ops.rglru_gates(gate_w, dev("p.ra.b").reshape(-1), dev("p.ri.b").reshape(-1), dev("p.lam"), dev("p.y.b"), u, proj, a, d, y)
         out = torch.empty(n, C, device=DEV)
         ops.rglru_scan(a, d, y, proj, dev("p.x.b"), _meta(entries), len(entries), state, out, K)
         return out.cpu()
@@ -348,6 +395,19 @@ def _noise(cfg, w, tokens):
     return float(d.max()), float(d.mean())
 
 
+CLOSE_CALL = 3e-3      # a choice score's lead below this is within what bfloat16 rounding moves a score by
+
+
+def _close_calls(cfg, w, tokens):
+    """Per position: True where some routed layer chooses its experts by a lead that bfloat16 rounding can overturn. There two
+    right implementations may choose different experts, and the position is held to the float32 engine alone."""
+    margins = []
+    plain.forward(cfg, w, tokens, margins=margins)
+    if not margins:
+        return torch.zeros(len(tokens), dtype=torch.bool)
+    return torch.stack(margins).min(0).values < CLOSE_CALL
+
+
 LENGTHS = {"X": [70, 130, 45, 33, 2], "Y": [300, 65, 140, 129, 40], "Z": [48, 90, 17, 64, 5]}
 
 
@@ -367,6 +427,7 @@ def test_replay_modes(name, dtype, ganupel_dirs, tmp_path):
     exact = [plain.forward(pcfg, w, r).float() for r in reqs]
     want = exact if rnd is None else [plain.forward(pcfg, w, r, rnd).float() for r in reqs]
     noise = [None if rnd is None else _noise(pcfg, w, r) for r in reqs]
+    close = [None if rnd is None else _close_calls(pcfg, w, r) for r in reqs]
     per = lambda n: -(-n // page) * page
     longest = sorted((per(len(r)) for r in reqs), reverse=True)
     pool = max(longest[0] + longest[1] + page, 4 * page)
@@ -376,6 +437,10 @@ def test_replay_modes(name, dtype, ganupel_dirs, tmp_path):
     def compare(got, i, a, b, what):
         tol = logit_tolerance(dtype, want[i]) if noise[i] is None else noise[i][0]
         diff = (got - want[i][a:b]).abs()
+        if close[i] is not None:
+            diff = diff[~close[i][a:b]]
+            if diff.numel() == 0:
+                return bits.check(i, a, got, f"{name} {what}")
         assert diff.max() <= tol, f"{name} {dtype} {what}: max |diff| {diff.max():.3e} > {tol:.3e} at {a + int(diff.max(dim=1).values.argmax())}"
         bits.check(i, a, got, f"{name} {what}")
 
