@@ -5,7 +5,7 @@
 //
 // The kernel takes q, g, k, v as columns of one float32 row per token, so whatever makes them is a kernel in front.
 // HGRN2 is one such maker (`hgrn2_activate_kernel`): q = silu(W_q x), g = l + (1 - l) sigmoid(W_f x + b) with a lower
-// bound l per channel, k = 1 - g (the forget gate also decides what is written), v = W_v x.
+// bound l per channel, k = 1 - g (the gate's complement is the key: what a channel does not keep, it takes in), v = W_v x.
 // Everything here is 32-bit. A CTA owns (request of the step, head, 32 value columns) and walks the request's tokens of
 // this step in order with the state in registers; it reads the state the step before left (or starts from zero at
 // position 0) and writes it back at the end. The D sums of an output are cut into parts of 16 consecutive elements, each

@@ -72,26 +72,27 @@ __global__ void rglru_conv_kernel(Proj proj, const TW* __restrict__ x_bias, cons
   u[static_cast<int64_t>(row) * C + c] = sum;
 }
 
-// The gates of kTT tokens for 32 channels of one block of channels. The block's inputs k are cut into four quarters (a function of
-// the block's size alone), a warp each; lane j of a warp adds, over its quarter in ascending order, gate_w[b][k][j] u[t][k] for r and
+// The gates of kTT tokens for up to kGateOutputs channels of one block of channels. The block's inputs k are cut into four quarters (a function of
+// the block's size alone), kGateOutputs / 32 warps each; a thread adds for its channel j, over its quarter in ascending order, gate_w[b][k][j] u[t][k] for r and
 // gate_w[b][k][bw + j] u[t][k] for i (the matrices lie transposed, so that a warp reads consecutive weights; the tokens' inputs
 // are broadcast from shared memory), one chain of fused multiply-adds per gate, token and quarter; the quarters are added in
 // ascending order. Nothing of that depends on the step: the same bits however many tokens it brings. Then a, the driven input
 // d = sqrt(1 - a^2) i u and y = gelu(W_y h + b_y).
-constexpr int kTT = 16, kQuarters = 4;
+constexpr int kTT = 16, kQuarters = 4, kGateOutputs = 64;
 
 template <class TG, class TW>
-__global__ void __launch_bounds__(32 * kQuarters) rglru_gates_kernel(const TG* __restrict__ gate_w, const TW* __restrict__ r_bias,
+__global__ void __launch_bounds__(kGateOutputs * kQuarters) rglru_gates_kernel(const TG* __restrict__ gate_w, const TW* __restrict__ r_bias,
                                                                       const TW* __restrict__ i_bias, const TW* __restrict__ lam,
                                                                       const float* __restrict__ u, Proj proj, const TW* __restrict__ y_bias,
                                                                       float* __restrict__ a_out, float* __restrict__ d_out, float* __restrict__ y_out,
                                                                       int n, int C, int bw) {
-  extern __shared__ __align__(16) float us[];         // [kTT][bw], then the quarters' sums [kQuarters][2][kTT][32]
+  extern __shared__ __align__(16) float us[];         // [kTT][bw], then the quarters' sums [kQuarters][2][kTT][outputs of the CTA]
   float* red = us + kTT * bw;
   sb::grid_launch_dependents();
   const int t0 = blockIdx.x * kTT, b = blockIdx.y;
   const int nt = min(kTT, n - t0);
-  const int lane = threadIdx.x & 31, quarter = threadIdx.x >> 5, j = blockIdx.z * 32 + lane;
+  const int outs = blockDim.x / kQuarters;            // channels of this CTA (a multiple of 32)
+  const int lane = threadIdx.x % outs, quarter = threadIdx.x / outs, j = blockIdx.z * outs + lane;
   sb::grid_dependency_wait();
   for (int i = threadIdx.x; i < kTT * bw; i += blockDim.x) {
     const int t = i / bw, k = i % bw;
@@ -127,8 +128,8 @@ __global__ void __launch_bounds__(32 * kQuarters) rglru_gates_kernel(const TG* _
   }
 #pragma unroll
   for (int t = 0; t < kTT; ++t) {
-    red[((quarter * 2 + 0) * kTT + t) * 32 + lane] = ar[t];
-    red[((quarter * 2 + 1) * kTT + t) * 32 + lane] = ai[t];
+    red[((quarter * 2 + 0) * kTT + t) * outs + lane] = ar[t];
+    red[((quarter * 2 + 1) * kTT + t) * outs + lane] = ai[t];
   }
   __syncthreads();
   if (j >= bw) return;
@@ -136,11 +137,11 @@ __global__ void __launch_bounds__(32 * kQuarters) rglru_gates_kernel(const TG* _
   const float rb = sb::widen(r_bias[c]), ib = sb::widen(i_bias[c]), l = sb::widen(lam[c]), yb = sb::widen(y_bias[c]);
   const float softplus = l > 20.0f ? l : log1pf(expf(l));
   for (int t = quarter; t < nt; t += kQuarters) {       // the tokens' epilogues are spread over the warps
-    float sr = red[(0 * kTT + t) * 32 + lane], si = red[(1 * kTT + t) * 32 + lane];
+    float sr = red[(0 * kTT + t) * outs + lane], si = red[(1 * kTT + t) * outs + lane];
 #pragma unroll
     for (int q = 1; q < kQuarters; ++q) {
-      sr += red[((q * 2 + 0) * kTT + t) * 32 + lane];
-      si += red[((q * 2 + 1) * kTT + t) * 32 + lane];
+      sr += red[((q * 2 + 0) * kTT + t) * outs + lane];
+      si += red[((q * 2 + 1) * kTT + t) * outs + lane];
     }
     const int64_t i = static_cast<int64_t>(t0 + t) * C + c;
     const float rg = 1.0f / (1.0f + expf(-(sr + rb)));
@@ -250,8 +251,9 @@ SB_EXPORT int sb_rglru_gates(const void* gate_w, int gate_dtype, const void* r_b
   if (bw > 2048) return sb::fail("sb_rglru_gates: blocks of %d channels (at most 2048)", bw);
   if (w_dtype != 0) return sb::fail("sb_rglru_gates: biases and lam are float32");
   const Proj pr{proj, n_partials, partial_stride};
-  const dim3 grid((n + kTT - 1) / kTT, blocks, (bw + 31) / 32), block(32 * kQuarters);
-  const size_t smem = sizeof(float) * (kTT * bw + kQuarters * 2 * kTT * 32);
+  const int outs = bw >= kGateOutputs ? kGateOutputs : (bw + 31) / 32 * 32;
+  const dim3 grid((n + kTT - 1) / kTT, blocks, (bw + outs - 1) / outs), block(outs * kQuarters);
+  const size_t smem = sizeof(float) * (kTT * bw + kQuarters * 2 * kTT * outs);
 #define SB_GATES(TG)                                                                                                                            \
   do {                                                                                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(rglru_gates_kernel<TG, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \

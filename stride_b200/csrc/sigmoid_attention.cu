@@ -162,15 +162,13 @@ __global__ void __launch_bounds__(kWarps * 32) sigmoid_attention_kernel(AttnPara
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // The bfloat16 form on the tensor cores (mma.sync.m16n8k16, float32 accumulation). A CTA of four warps owns 64 rows of one
-// key/value head: the 64 / Hg consecutive positions of one entry times the Hg query heads of the group, 16 rows a warp. It walks
-// the tiles of 64 keys (cut by ABSOLUTE position) that any of its rows sees, in ascending order: S = Q K^T, the weights
+// key/value head: the 64 / Hg consecutive positions of one entry times the Hg query heads of the group, 16 rows a warp (a CTA of one
+// warp: 16 rows). It walks the tiles of keys (cut by ABSOLUTE position) that any of its rows sees, in ascending order: S = Q K^T, the weights
 // sigmoid(scale S + bias) in 32-bit with 0 for keys a row does not see, each weight split into two bfloat16 parts hi + lo
 // (|w - hi - lo| <= 2^-17 w), O += hi V + lo V. A key that a row does not see adds exact zeros, so a row's result depends on its
-// own position alone: a token has the same bits in a prompt, in a portion and decoded alone (where 64 / Hg - 1 positions of the
-// tile are empty; the step is bound by the keys' and values' bytes then, not by the products).
+// own position alone: a token has the same bits in a prompt, in a portion and decoded alone.
 // Needs key sizes that are a multiple of 16 up to 256, value sizes that are a multiple of 16 up to 128 and a power of two up to 16 of
 // query heads a key head; everything else takes sigmoid_attention_kernel.
-constexpr int kTile = 64;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -207,15 +205,20 @@ struct TileParams {
   float scale;
 };
 
-template <int NV>   // value size / 16
-__global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_kernel(TileParams p) {
+// NV: value size / 16. WARPS: warps of the CTA, 16 rows each (the same instructions on the same operands for a row whatever it is, so the
+// same bits). KT: keys of a staged tile (a multiple of 16; the sum over the keys is a chain over steps of 16 keys in ascending order whatever KT is).
+template <int NV, int WARPS, int KT>
+__global__ void __launch_bounds__(32 * WARPS, WARPS == 1 ? 8 : (NV <= 4 ? 4 : 2)) sigmoid_attention_tile_kernel(TileParams p) {
   extern __shared__ __align__(16) unsigned char raw[];
+  constexpr int kRows = 16 * WARPS, NS = KT / 8, NK = KT / 16;
+  static_assert(KT <= 32 * WARPS && KT % 16 == 0, "a thread per key row of a tile");
   sb::grid_launch_dependents();
-  const int Hg = p.H / p.G, PT = kTile / Hg, g = blockIdx.y;
+  const int Hg = p.H / p.G, PT = kRows / Hg, g = blockIdx.y;
   const int ldk = p.D + 8, ldv = p.Dv + 8;                      // padded rows: ldmatrix without bank conflicts
-  bf16* Qs = reinterpret_cast<bf16*>(raw);                      // [64][ldk]
-  bf16* stage0 = Qs + kTile * ldk;                              // two staging buffers of keys [64][ldk] and values [64][ldv]
-  const int stage_elems = kTile * (ldk + ldv);
+  const bf16** rowptr = reinterpret_cast<const bf16**>(raw);    // [2][KT]: where a tile's key rows lie (null: a row nobody sees)
+  bf16* Qs = reinterpret_cast<bf16*>(raw + 2 * KT * sizeof(void*));   // [kRows][ldk]
+  bf16* stage0 = Qs + kRows * ldk;                              // two staging buffers of keys [KT][ldk] and values [KT][ldv]
+  const int stage_elems = KT * (ldk + ldv);
   // which entry and which tile of its positions this CTA is
   int e = 0, tile = blockIdx.x, len = 0;
   for (; e < p.entries; ++e) {
@@ -233,17 +236,13 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   sb::grid_dependency_wait();
   // Q: row r = (position t0 + r / Hg, head g Hg + r % Hg); rows beyond the entry are zero
-  const int dchunks = p.D / 8;
-  for (int i = threadIdx.x; i < kTile * dchunks; i += blockDim.x) {
+  const int dchunks = p.D / 8, vchunks = p.Dv / 8, cpr = dchunks + vchunks;
+  for (int i = threadIdx.x; i < kRows * dchunks; i += blockDim.x) {
     const int r = i / dchunks, c = i % dchunks, t = r / Hg;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (t < nt) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(row0 + t0 + t) * p.H + g * Hg + r % Hg) * p.D + c * 8);
     *reinterpret_cast<uint4*>(Qs + r * ldk + c * 8) = v;
   }
-  // (A warp none of whose 16 rows exists, as with a decoded token, which fills the first Hg rows of the tile only, multiplies all the
-  // same: leaving it out made the step slower, 0.196 against 0.128 ms for 64 decoded tokens over 1,024 keys, since the one warp with rows
-  // then is what every barrier of the CTA waits for.)
-  constexpr bool active = true;
   const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
   const int p_lo = r_lo / Hg < nt ? first_pos + r_lo / Hg : -1, p_hi = r_hi / Hg < nt ? first_pos + r_hi / Hg : -1;
   const float b_lo = p.bias != nullptr ? p.bias[g * Hg + r_lo % Hg] : 0.0f, b_hi = p.bias != nullptr ? p.bias[g * Hg + r_hi % Hg] : 0.0f;
@@ -251,26 +250,34 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
 #pragma unroll
   for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   const bf16* base = p.pages + static_cast<int64_t>(g) * p.head_stride;
-  const int vchunks = p.Dv / 8;
+  // the copies of a row are spread over `per_row` threads (a power of two), so that no copy costs a division
+  int per_row = 1, shift = 0;
+  while (per_row < cpr && per_row < 32) {
+    per_row <<= 1;
+    ++shift;
+  }
   // a tile's keys and values are requested (asynchronous copies) while the tile before is multiplied
   auto request = [&](int kt, int buf) {
+    if (threadIdx.x < KT) {
+      const int j = kt * KT + threadIdx.x;
+      rowptr[buf * KT + threadIdx.x] = (j >= first_key && j <= last_pos)
+          ? base + static_cast<int64_t>(table[j / p.page_size]) * p.page_stride + static_cast<int64_t>(j % p.page_size) * p.Dc : nullptr;
+    }
+    __syncthreads();
     bf16* Ks = stage0 + buf * stage_elems;
-    bf16* Vs = Ks + kTile * ldk;
-    for (int i = threadIdx.x; i < kTile * (dchunks + vchunks); i += blockDim.x) {
-      const int r = i / (dchunks + vchunks), c = i % (dchunks + vchunks), j = kt * kTile + r;
-      const bool is_v = c >= dchunks;
-      bf16* dst = is_v ? Vs + r * ldv + (c - dchunks) * 8 : Ks + r * ldk + c * 8;
-      if (j >= first_key && j <= last_pos) {
-        const bf16* src = base + static_cast<int64_t>(table[j / p.page_size]) * p.page_stride + static_cast<int64_t>(j % p.page_size) * p.Dc +
-                          (is_v ? p.v_offset + (c - dchunks) * 8 : c * 8);
-        copy16(dst, src);
-      } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    bf16* Vs = Ks + KT * ldk;
+    for (int r = threadIdx.x >> shift; r < KT; r += blockDim.x >> shift) {
+      const bf16* src = rowptr[buf * KT + r];
+      for (int c = threadIdx.x & (per_row - 1); c < cpr; c += per_row) {
+        const bool is_v = c >= dchunks;
+        bf16* dst = is_v ? Vs + r * ldv + (c - dchunks) * 8 : Ks + r * ldk + c * 8;
+        if (src != nullptr) copy16(dst, src + (is_v ? p.v_offset + (c - dchunks) * 8 : c * 8));
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const int kt_first = first_key / kTile, kt_last = last_pos / kTile;
+  const int kt_first = first_key / KT, kt_last = last_pos / KT;
   request(kt_first, 0);
   for (int kt = kt_first; kt <= kt_last; ++kt) {
     const int buf = (kt - kt_first) & 1;
@@ -282,17 +289,16 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
     }
     __syncthreads();
     const bf16* Ks = stage0 + buf * stage_elems;
-    const bf16* Vs = Ks + kTile * ldk;
-    if (active) {
-    // S = Q K^T for this warp's 16 rows and the tile's 64 keys
-    float s[8][4];
+    const bf16* Vs = Ks + KT * ldk;
+    // S = Q K^T for this warp's 16 rows and the tile's keys
+    float s[NS][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int i = 0; i < NS; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
     for (int k0 = 0; k0 < p.D; k0 += 16) {
       uint32_t a[4];
       ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * ldk + k0 + (lane >> 4) * 8);
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {                             // two n8 tiles of keys at a time
+      for (int n = 0; n < NS / 2; ++n) {                        // two n8 tiles of keys at a time
         uint32_t b[4];
         ldmatrix_x4(b, Ks + (n * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + k0 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * n], a, b[0], b[1]);
@@ -300,13 +306,13 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
       }
     }
     // the weights, split in two bfloat16 parts, as A operands of the value product
-    uint32_t hi[4][4], lo[4][4];
+    uint32_t hi[NK][4], lo[NK][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < NS; ++n) {
       float w[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int j = kt * kTile + n * 8 + (lane & 3) * 2 + (c & 1);
+        const int j = kt * KT + n * 8 + (lane & 3) * 2 + (c & 1);
         const int pos = c < 2 ? p_lo : p_hi;
         const bool seen = j <= pos && (p.window <= 0 || pos - j < p.window);
         const float x = fmaf(s[n][c], p.scale, c < 2 ? b_lo : b_hi);
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
     }
     // O += hi V + lo V
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
+    for (int kk = 0; kk < NK; ++kk) {
 #pragma unroll
       for (int nv = 0; nv < NV; ++nv) {
         uint32_t b[4];
@@ -331,7 +337,6 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
         mma_bf16(o[2 * nv + 1], hi[kk], b[2], b[3]);
         mma_bf16(o[2 * nv + 1], lo[kk], b[2], b[3]);
       }
-    }
     }
     __syncthreads();                      // this tile's buffer may be written again
   }
@@ -346,17 +351,25 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 2) sigmoid_attention_tile_k
   }
 }
 
-template <int NV>
-int launch_tiles(const TileParams& p, int n, cudaStream_t stream) {
-  const int Hg = p.H / p.G, PT = kTile / Hg;
-  const size_t smem = sizeof(bf16) * kTile * (3 * (p.D + 8) + 2 * (p.Dv + 8));
+template <int NV, int WARPS, int KT>
+int launch_tiles_of(const TileParams& p, int n, cudaStream_t stream) {
+  const int Hg = p.H / p.G, PT = 16 * WARPS / Hg;
+  const size_t smem = 2 * KT * sizeof(void*) + sizeof(bf16) * (16 * WARPS * (p.D + 8) + 2 * KT * (p.D + 8 + p.Dv + 8));
   static sb::DeviceOnce once;
   if (once.needed()) {
-    cudaFuncSetAttribute(sigmoid_attention_tile_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(sigmoid_attention_tile_kernel<NV, WARPS, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     once.done();
   }
-  sb::launch_pdl(sigmoid_attention_tile_kernel<NV>, dim3((n + PT - 1) / PT + p.entries, p.G), dim3(128), smem, stream, p);
+  sb::launch_pdl(sigmoid_attention_tile_kernel<NV, WARPS, KT>, dim3((n + PT - 1) / PT + p.entries, p.G), dim3(32 * WARPS), smem, stream, p);
   return sb::check_launch("sb_sigmoid_attention_tiles");
+}
+
+// CTAs of four warps with tiles of 64 keys for every step. (Steps of decoded tokens only, whose Hg rows fill a sixteenth of such a CTA's
+// rows, were tried on CTAs of one warp with tiles of 32 keys, which give the same bits: 0.154 ms against 0.128 for 64 decoded tokens over
+// 1,024 keys. The 512 (entry, key head) pairs are then 3.5 warps an SM, each a chain of dependent copies, products and exponentials.)
+template <int NV>
+int launch_tiles(const TileParams& p, int n, cudaStream_t stream) {
+  return launch_tiles_of<NV, 4, 64>(p, n, stream);
 }
 
 }  // namespace

@@ -1,4 +1,4 @@
-"""HGRN2 as a mixer with a state per request: linear attention whose forget gate also decides what is written.
+"""HGRN2 as a mixer with a state per request: linear attention in which the complement of the forget gate is the key (what a channel does not keep, it takes in).
 
 Per head, for a token t: q = silu(W_q x) [key_dim], v = W_v x [value_dim], f = l + (1 - l) sigmoid(W_f x + b) with a
 lower bound l per channel; S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t; every head's o is RMS-normed on

@@ -82,7 +82,7 @@ def sigmoid_window_attention(h, tensors, prefix, m, rnd=None):
 
 
 def hgrn2(h, tensors, prefix, m, eps, rnd=None):
-    """Linear attention whose forget gate f also writes: S <- diag(f) S + (1 - f) v^T, o = S^T q."""
+    """Linear attention with the key tied to the forget gate f, k = 1 - f: S <- diag(f) S + (1 - f) v^T, o = S^T q."""
     T = h.shape[0]
     H, D, V = m["heads"], m["dim"], m["vdim"]
     q = silu(h @ w(tensors, prefix + "q").T).view(T, H, D)
