@@ -351,6 +351,176 @@ __global__ void __launch_bounds__(32 * WARPS, WARPS == 1 ? 8 : (NV <= 4 ? 4 : 2)
   }
 }
 
+// Steps of decoded tokens only: an entry's Hg rows fill one 16-row tile, and the four warps of a CTA share it instead of multiplying empty
+// rows. Warp w makes the scores and weights of keys 16 w .. 16 w + 15 of a tile, which are exactly the A operand of step w of the value
+// product; the warps exchange these operands through shared memory, and warp w then owns the value columns 16 (w + 4 i) ..: its sums run
+// over the tile's four steps in ascending order, the first part of a weight before the second. Every score, weight and sum is made by the
+// instructions that make it in sigmoid_attention_tile_kernel, on the same operands in the same order: the same bits, with a quarter of
+// the instructions a CTA.
+template <int NV>
+__global__ void __launch_bounds__(128, 4) sigmoid_attention_decode_kernel(TileParams p) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  constexpr int KT = 64, NK = KT / 16, NVW = (NV + 3) / 4;
+  sb::grid_launch_dependents();
+  const int Hg = p.H / p.G, PT = 16 / Hg, g = blockIdx.y;
+  const int ldk = p.D + 8, ldv = p.Dv + 8;
+  const bf16** rowptr = reinterpret_cast<const bf16**>(raw);    // [2][KT]
+  uint32_t* Ps = reinterpret_cast<uint32_t*>(raw + 2 * KT * sizeof(void*));   // [2 parts][NK steps][4 registers][32 lanes]
+  bf16* Qs = reinterpret_cast<bf16*>(Ps + 2 * NK * 4 * 32);     // [16][ldk]
+  bf16* stage0 = Qs + 16 * ldk;
+  const int stage_elems = KT * (ldk + ldv);
+  int e = 0, tile = blockIdx.x, len = 0;
+  for (; e < p.entries; ++e) {
+    len = p.meta[2 * p.meta_stride + e];
+    const int tiles = (len + PT - 1) / PT;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (e >= p.entries) return;
+  const int slot = p.meta[e], row0 = p.meta[p.meta_stride + e], pos0 = p.meta[3 * p.meta_stride + e];
+  const int t0 = tile * PT, nt = min(PT, len - t0);
+  const int first_pos = pos0 + t0, last_pos = first_pos + nt - 1;
+  const int first_key = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  sb::grid_dependency_wait();
+  const int dchunks = p.D / 8, vchunks = p.Dv / 8, cpr = dchunks + vchunks;
+  for (int i = threadIdx.x; i < 16 * dchunks; i += blockDim.x) {
+    const int r = i / dchunks, c = i % dchunks, t = r / Hg;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < nt) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(row0 + t0 + t) * p.H + g * Hg + r % Hg) * p.D + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * ldk + c * 8) = v;
+  }
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+  const int p_lo = r_lo / Hg < nt ? first_pos + r_lo / Hg : -1, p_hi = r_hi / Hg < nt ? first_pos + r_hi / Hg : -1;
+  const float b_lo = p.bias != nullptr ? p.bias[g * Hg + r_lo % Hg] : 0.0f, b_hi = p.bias != nullptr ? p.bias[g * Hg + r_hi % Hg] : 0.0f;
+  float o[2 * NVW][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NVW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  const bf16* base = p.pages + static_cast<int64_t>(g) * p.head_stride;
+  int per_row = 1, shift = 0;
+  while (per_row < cpr && per_row < 32) {
+    per_row <<= 1;
+    ++shift;
+  }
+  auto request = [&](int kt, int buf) {
+    if (threadIdx.x < KT) {
+      const int j = kt * KT + threadIdx.x;
+      rowptr[buf * KT + threadIdx.x] = (j >= first_key && j <= last_pos)
+          ? base + static_cast<int64_t>(table[j / p.page_size]) * p.page_stride + static_cast<int64_t>(j % p.page_size) * p.Dc : nullptr;
+    }
+    __syncthreads();
+    bf16* Ks = stage0 + buf * stage_elems;
+    bf16* Vs = Ks + KT * ldk;
+    for (int r = threadIdx.x >> shift; r < KT; r += blockDim.x >> shift) {
+      const bf16* src = rowptr[buf * KT + r];
+      for (int c = threadIdx.x & (per_row - 1); c < cpr; c += per_row) {
+        const bool is_v = c >= dchunks;
+        bf16* dst = is_v ? Vs + r * ldv + (c - dchunks) * 8 : Ks + r * ldk + c * 8;
+        if (src != nullptr) copy16(dst, src + (is_v ? p.v_offset + (c - dchunks) * 8 : c * 8));
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int kt_first = first_key / KT, kt_last = last_pos / KT;
+  request(kt_first, 0);
+  for (int kt = kt_first; kt <= kt_last; ++kt) {
+    const int buf = (kt - kt_first) & 1;
+    if (kt < kt_last) {
+      request(kt + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const bf16* Ks = stage0 + buf * stage_elems;
+    const bf16* Vs = Ks + KT * ldk;
+    // the scores of this warp's 16 keys
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int k0 = 0; k0 < p.D; k0 += 16) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, Qs + (lane & 15) * ldk + k0 + (lane >> 4) * 8);
+      ldmatrix_x4(b, Ks + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ldk + k0 + ((lane >> 3) & 1) * 8);
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+    }
+    // their weights in two parts: the A operand of step `warp` of the value product, handed to the other warps
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      float w[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = kt * KT + warp * 16 + n * 8 + (lane & 3) * 2 + (c & 1);
+        const int pos = c < 2 ? p_lo : p_hi;
+        const bool seen = j <= pos && (p.window <= 0 || pos - j < p.window);
+        const float x = fmaf(s[n][c], p.scale, c < 2 ? b_lo : b_hi);
+        w[c] = seen ? __fdividef(1.0f, 1.0f + __expf(-x)) : 0.0f;
+      }
+      const __nv_bfloat162 h01 = __floats2bfloat162_rn(w[0], w[1]), h23 = __floats2bfloat162_rn(w[2], w[3]);
+      uint32_t* hi = Ps + ((0 * NK + warp) * 4 + n * 2) * 32 + lane;
+      uint32_t* lo = Ps + ((1 * NK + warp) * 4 + n * 2) * 32 + lane;
+      hi[0] = *reinterpret_cast<const uint32_t*>(&h01);
+      hi[32] = *reinterpret_cast<const uint32_t*>(&h23);
+      lo[0] = pack_bf16(w[0] - __low2float(h01), w[1] - __high2float(h01));
+      lo[32] = pack_bf16(w[2] - __low2float(h23), w[3] - __high2float(h23));
+    }
+    __syncthreads();
+    // O += hi V + lo V for this warp's value columns, the tile's steps in ascending order
+#pragma unroll
+    for (int kk = 0; kk < NK; ++kk) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        hi[i] = Ps[((0 * NK + kk) * 4 + i) * 32 + lane];
+        lo[i] = Ps[((1 * NK + kk) * 4 + i) * 32 + lane];
+      }
+#pragma unroll
+      for (int i = 0; i < NVW; ++i) {
+        const int nv = warp + 4 * i;
+        if (nv < NV) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + nv * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * i], hi, b[0], b[1]);
+          mma_bf16(o[2 * i], lo, b[0], b[1]);
+          mma_bf16(o[2 * i + 1], hi, b[2], b[3]);
+          mma_bf16(o[2 * i + 1], lo, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();                      // the tile's buffer and the exchanged operands may be written again
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r_hi : r_lo;
+    if (r / Hg >= nt) continue;
+    bf16* dst = p.out + (static_cast<int64_t>(row0 + t0 + r / Hg) * p.H + g * Hg + r % Hg) * p.Dv + (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < NVW; ++i) {
+      const int nv = warp + 4 * i;
+      if (nv < NV) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + nv * 16) = __floats2bfloat162_rn(o[2 * i][2 * half], o[2 * i][2 * half + 1]);
+        *reinterpret_cast<__nv_bfloat162*>(dst + nv * 16 + 8) = __floats2bfloat162_rn(o[2 * i + 1][2 * half], o[2 * i + 1][2 * half + 1]);
+      }
+    }
+  }
+}
+
+template <int NV>
+int launch_decode(const TileParams& p, int n, cudaStream_t stream) {
+  const int Hg = p.H / p.G, PT = 16 / Hg;
+  const size_t smem = 2 * 64 * sizeof(void*) + 2 * 4 * 4 * 32 * sizeof(uint32_t) + sizeof(bf16) * (16 * (p.D + 8) + 2 * 64 * (p.D + 8 + p.Dv + 8));
+  static sb::DeviceOnce once;
+  if (once.needed()) {
+    cudaFuncSetAttribute(sigmoid_attention_decode_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    once.done();
+  }
+  sb::launch_pdl(sigmoid_attention_decode_kernel<NV>, dim3((n + PT - 1) / PT + p.entries, p.G), dim3(128), smem, stream, p);
+  return sb::check_launch("sb_sigmoid_attention_tiles");
+}
+
 template <int NV, int WARPS, int KT>
 int launch_tiles_of(const TileParams& p, int n, cudaStream_t stream) {
   const int Hg = p.H / p.G, PT = 16 * WARPS / Hg;
@@ -364,12 +534,13 @@ int launch_tiles_of(const TileParams& p, int n, cudaStream_t stream) {
   return sb::check_launch("sb_sigmoid_attention_tiles");
 }
 
-// CTAs of four warps with tiles of 64 keys for every step. (Steps of decoded tokens only, whose Hg rows fill a sixteenth of such a CTA's
-// rows, were tried on CTAs of one warp with tiles of 32 keys, which give the same bits: 0.154 ms against 0.128 for 64 decoded tokens over
-// 1,024 keys. The 512 (entry, key head) pairs are then 3.5 warps an SM, each a chain of dependent copies, products and exponentials.)
+// Steps with a prompt portion: CTAs of four warps with 64 rows. Steps of decoded tokens only: the four warps share one tile of 16 rows.
+// (Such steps were also tried on the 64-row CTAs, whose empty rows are multiplied all the same, and on CTAs of one warp with tiles of 32
+// keys: 0.111 and 0.154 ms for 64 decoded tokens over 1,024 keys; the latter are 3.5 warps an SM, each a chain of dependent copies,
+// products and exponentials. All give the same bits.)
 template <int NV>
 int launch_tiles(const TileParams& p, int n, cudaStream_t stream) {
-  return launch_tiles_of<NV, 4, 64>(p, n, stream);
+  return n == p.entries ? launch_decode<NV>(p, n, stream) : launch_tiles_of<NV, 4, 64>(p, n, stream);
 }
 
 }  // namespace
