@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kGateOutputs * kQuarters) rglru_gates_kernel(c
                                                                       const float* __restrict__ u, Proj proj, const TW* __restrict__ y_bias,
                                                                       float* __restrict__ a_out, float* __restrict__ d_out, float* __restrict__ y_out,
                                                                       int n, int C, int bw) {
-  extern __shared__ __align__(16) float us[];         // [kTT][bw], then the quarters' sums [kQuarters][2][kTT][outputs of the CTA]
+  extern __shared__ __align__(16) float us[];         // [bw][kTT] (an input's tokens side by side: four 16-byte reads an input), then the quarters' sums [kQuarters][2][kTT][outputs of the CTA]
   float* red = us + kTT * bw;
   sb::grid_launch_dependents();
   const int t0 = blockIdx.x * kTT, b = blockIdx.y;
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(kGateOutputs * kQuarters) rglru_gates_kernel(c
   sb::grid_dependency_wait();
   for (int i = threadIdx.x; i < kTT * bw; i += blockDim.x) {
     const int t = i / bw, k = i % bw;
-    us[i] = t < nt ? u[static_cast<int64_t>(t0 + t) * C + b * bw + k] : 0.0f;
+    us[k * kTT + t] = t < nt ? u[static_cast<int64_t>(t0 + t) * C + b * bw + k] : 0.0f;
   }
   __syncthreads();
   const int per = (bw + kQuarters - 1) / kQuarters, k_begin = quarter * per, k_end = min(bw, k_begin + per);
@@ -117,11 +117,18 @@ __global__ void __launch_bounds__(kGateOutputs * kQuarters) rglru_gates_kernel(c
 #pragma unroll
       for (int i = 0; i < kAhead; ++i) {
         if (k0 + i >= k_end) break;
+        const float4* x4 = reinterpret_cast<const float4*>(us + (k0 + i) * kTT);
 #pragma unroll
-        for (int t = 0; t < kTT; ++t) {
-          const float x = us[t * bw + k0 + i];
-          ar[t] = fmaf(wr[i], x, ar[t]);
-          ai[t] = fmaf(wi[i], x, ai[t]);
+        for (int t = 0; t < kTT / 4; ++t) {
+          const float4 x = x4[t];
+          ar[4 * t] = fmaf(wr[i], x.x, ar[4 * t]);
+          ai[4 * t] = fmaf(wi[i], x.x, ai[4 * t]);
+          ar[4 * t + 1] = fmaf(wr[i], x.y, ar[4 * t + 1]);
+          ai[4 * t + 1] = fmaf(wi[i], x.y, ai[4 * t + 1]);
+          ar[4 * t + 2] = fmaf(wr[i], x.z, ar[4 * t + 2]);
+          ai[4 * t + 2] = fmaf(wi[i], x.z, ai[4 * t + 2]);
+          ar[4 * t + 3] = fmaf(wr[i], x.w, ar[4 * t + 3]);
+          ai[4 * t + 3] = fmaf(wi[i], x.w, ai[4 * t + 3]);
         }
       }
     }
@@ -148,7 +155,7 @@ __global__ void __launch_bounds__(kGateOutputs * kQuarters) rglru_gates_kernel(c
     const float ig = 1.0f / (1.0f + expf(-(si + ib)));
     const float log_a = -8.0f * rg * softplus;
     a_out[i] = expf(log_a);
-    d_out[i] = sqrtf(-expm1f(2.0f * log_a)) * (ig * us[t * bw + j]);
+    d_out[i] = sqrtf(-expm1f(2.0f * log_a)) * (ig * us[j * kTT + t]);
     y_out[i] = gelu_tanh(folded(proj.p + static_cast<int64_t>(t0 + t) * 2 * C + c, proj.n_partials, proj.stride) + yb);
   }
 }
