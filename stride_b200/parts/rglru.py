@@ -69,7 +69,7 @@ class RGLRUMixer(Mixer):
         return {"rglru", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
 
     def forward(self, ctx, x, stream, cache):
-        n, ws, C, bw = ctx.n, ctx.workspace, self.width, self.bw
+        n, ws, C = ctx.n, ctx.workspace, self.width
         proj = self.proj.forward_partials(x, ws.raw("rglru.proj", (self.proj.partial_elems(ws.max_tokens),), torch.float32))
         u = ws.get("rglru.u", n, (C,), torch.float32)
         ops.rglru_conv(proj, self.x_bias, self.conv, self.conv_bias, ctx.positions, ctx.slots, cache.state, u)
@@ -80,7 +80,7 @@ class RGLRUMixer(Mixer):
         self.o.forward_add(out, stream, ws.raw("rglru.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
 
     def emit(self, program, x, cache):
-        ws, C, bw = program.workspace, self.width, self.bw
+        ws, C = program.workspace, self.width
         T, f32 = ws.max_tokens, torch.float32
         proj = ws.raw("rglru.proj", (self.proj.partial_elems(T),), f32)
         S = self.proj.emit_partials(program, x, proj)

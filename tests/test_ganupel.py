@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_ganupel as plain
-from ganupel_cases import GANUPEL, GANUPEL_X, GANUPEL_Y, GANUPEL_Z
+from ganupel_cases import GANUPEL, GANUPEL_X, GANUPEL_Z
 
 F = torch.float64
 

@@ -5,14 +5,13 @@ decoding; batches against each request alone; greedy generation through the entr
 from __future__ import annotations
 
 import copy
-import math
 
 import pytest
 import torch
 
 import plain_ganupel as plain
 from conftest import TraceRun, logit_tolerance, random_tokens
-from ganupel_cases import GANUPEL, load_plain, remember_longer, write_model
+from ganupel_cases import GANUPEL, load_plain, write_model
 from test_replay_gpu import _Bits, _portions
 
 pytestmark = pytest.mark.gpu
