@@ -553,6 +553,37 @@ def _ganupel_kernels(timed, pk: dict, width: int, ff: int) -> dict:
                fraction_of_measured_bf16=round(6.0 * keys * Hq * Dh / ms / 1e9 / pk["bf16_tflops"], 4))
         ms = timed(lambda: ops.sigmoid_attention(q, o, pages, table, pos, slot, bias, Hq, G, Dh, Dh, window, 0.125), 3, clear=True)
         record("sigmoid_attention_block_per_token_" + label, ms, flops=4.0 * keys * Hq * Dh, moved=moved)
+    # the kernels in front of the recurrences and of attention, for a prompt of 2,048 tokens and for 64 decoded tokens
+    C, K, B = width, 4, width // 128
+    bw = C // B
+    gate_w = (torch.randn(B, bw, 2 * bw, device=dev) * 0.05).to(torch.bfloat16)
+    vecs = [torch.randn(C, device=dev) * 0.1 for _ in range(5)]
+    taps = torch.randn(C, K, device=dev)
+    for n in (2048, 64):
+        entries = 1 if n == 2048 else n
+        pr = torch.randn(1, n, 2 * C, device=dev)
+        rec = torch.zeros(entries + 1, K, C, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev) if entries == 1 else torch.full((n,), 9, dtype=torch.int32, device=dev)
+        slot = torch.zeros(n, dtype=torch.int32, device=dev) if entries == 1 else torch.arange(n, dtype=torch.int32, device=dev)
+        u, a_, d_, y_ = (torch.empty(n, C, device=dev) for _ in range(4))
+        ms = timed(lambda: ops.rglru_conv(pr, vecs[0], taps, vecs[1], pos, slot, rec, u), 5, clear=True)
+        record(f"rglru_conv_{n}", ms, n * C * 12.0)
+        ms = timed(lambda: ops.rglru_gates(gate_w, vecs[2], vecs[3], vecs[4], vecs[0], u, pr, a_, d_, y_), 5, clear=True)
+        record(f"rglru_gates_{n}", ms, flops=4.0 * n * C * bw, moved=n * C * 20.0 + gate_w.numel() * 2.0)
+        wq = Hq * Dh + 2 * G * Dh
+        qkv = torch.randn(1, n, wq, device=dev)
+        cs = torch.rand(4096, Dh // 2, 2, device=dev)
+        per = (n if entries == 1 else 10 + page - 1) // page + 1
+        pages = torch.zeros(entries * per + 1, 2, G, page, Dh, dtype=torch.bfloat16, device=dev)
+        table = torch.arange(entries * per, dtype=torch.int32, device=dev).view(entries, per)
+        q = torch.empty(n, Hq * Dh, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.qkv_rotate_append(qkv, pos, slot, cs, Dh, q, pages, table, Hq, G, Dh, Dh), 5, clear=True)
+        record(f"qkv_rotate_append_{n}", ms, n * wq * 6.0)
+        HD = H * D
+        proj = torch.randn(1, n, 2 * HD + H * V, device=dev)
+        act = torch.empty(n, 3 * HD + H * V, device=dev)
+        ms = timed(lambda: ops.hgrn2_activate(proj, vecs[0], vecs[1], act, HD, H * V), 5, clear=True)
+        record(f"hgrn2_activate_{n}", ms, n * (5 * HD + 2 * H * V) * 4.0)
     # between the products of the feed-forwards
     for n in (64, 2048):
         up = torch.randn(1, n, ff, device=dev)

@@ -89,6 +89,78 @@ __global__ void qkv_rotate_append_kernel(AppendParams p) {
   }
 }
 
+// Four consecutive elements a thread, for sizes and a rotated range that are multiples of four (so that the four and their four
+// partners lie in one head, and every request is 16 bytes). Same arithmetic as qkv_rotate_append_kernel: equal bits.
+__device__ __forceinline__ float4 folded4(const float* p, int n_partials, int64_t stride) {
+  float4 part[kInFlight];
+#pragma unroll
+  for (int s = 0; s < kInFlight; ++s)
+    if (s < n_partials) part[s] = *reinterpret_cast<const float4*>(p + s * stride);
+  float4 sum = part[0];
+#pragma unroll
+  for (int s = 1; s < kInFlight; ++s)
+    if (s < n_partials) sum = make_float4(sum.x + part[s].x, sum.y + part[s].y, sum.z + part[s].z, sum.w + part[s].w);
+  for (int s = kInFlight; s < n_partials; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(p + s * stride);
+    sum = make_float4(sum.x + v.x, sum.y + v.y, sum.z + v.z, sum.w + v.w);
+  }
+  return sum;
+}
+template <class T>
+__device__ __forceinline__ void store4(T* dst, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <class TQ, class TKV>
+__global__ void qkv_rotate_append_vec_kernel(AppendParams p) {
+  sb::grid_launch_dependents();
+  const int row = blockIdx.x;
+  const int nq = p.Hq * p.D, nk = p.Hkv * p.D, width = nq + nk + p.Hkv * p.Dv;
+  const int item = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const int pos = p.positions[row], slot = p.slots[row];
+  int page = 0;
+  if (p.write_kv && item >= nq && item < width) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+  sb::grid_dependency_wait();
+  if (item >= width) return;
+  const float* src = p.qkv + static_cast<int64_t>(row) * width;
+  float4 a = folded4(src + item, p.n_partials, p.partial_stride);
+  const int rh = p.rotary_dim / 2;
+  if (item < nq + nk) {
+    const int d = item % p.D;
+    if (d < p.rotary_dim) {
+      const bool low = d < rh;
+      const int j = low ? d : d - rh;
+      const float4 b = folded4(src + (low ? item + rh : item - rh), p.n_partials, p.partial_stride);
+      const float4* cs = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(pos) * rh + j) * 2);
+      const float4 c01 = cs[0], c23 = cs[1];      // (cos, sin) of pairs j, j + 1 and j + 2, j + 3
+      if (low) {
+        a = make_float4(__fsub_rn(__fmul_rn(a.x, c01.x), __fmul_rn(b.x, c01.y)), __fsub_rn(__fmul_rn(a.y, c01.z), __fmul_rn(b.y, c01.w)),
+                        __fsub_rn(__fmul_rn(a.z, c23.x), __fmul_rn(b.z, c23.y)), __fsub_rn(__fmul_rn(a.w, c23.z), __fmul_rn(b.w, c23.w)));
+      } else {
+        a = make_float4(__fadd_rn(__fmul_rn(a.x, c01.x), __fmul_rn(b.x, c01.y)), __fadd_rn(__fmul_rn(a.y, c01.z), __fmul_rn(b.y, c01.w)),
+                        __fadd_rn(__fmul_rn(a.z, c23.x), __fmul_rn(b.z, c23.y)), __fadd_rn(__fmul_rn(a.w, c23.z), __fmul_rn(b.w, c23.w)));
+      }
+    }
+  }
+  if (item < nq) {
+    store4<TQ>(static_cast<TQ*>(p.q_out) + static_cast<int64_t>(row) * nq + item, a);
+  } else if (p.write_kv) {
+    const bool is_v = item >= nq + nk;
+    const int e = is_v ? item - nq - nk : item - nq;
+    const int dim = is_v ? p.Dv : p.D, head = e / dim, d = e % dim;
+    store4<TKV>(static_cast<TKV*>(p.pages) + static_cast<int64_t>(page) * p.page_stride + (is_v ? p.v_offset : 0) +
+                    static_cast<int64_t>(head) * p.head_stride + static_cast<int64_t>(pos % p.page_size) * p.Dc + d, a);
+  }
+}
+
 struct AttnParams {
   const void* q;             // [n][H D]
   void* out;                 // [n][H Dv]
@@ -556,10 +628,19 @@ SB_EXPORT int sb_qkv_rotate_append(const float* qkv, int n_partials, int64_t par
   AppendParams p{qkv, n_partials, partial_stride, positions, slots, cos_sin, rotary_dim, q_out, pages, block_table, max_pages, page_size,
                  page_stride, v_offset, head_stride, Hq, Hkv, D, Dv, Dc, write_kv};
   const int width = Hq * D + Hkv * D + Hkv * Dv;
-  const dim3 grid(n, (width + 255) / 256);
-  if (q_dtype == 0 && kv_dtype == 0) sb::launch_pdl(qkv_rotate_append_kernel<float, float>, grid, dim3(256), 0, stream, p);
-  else if (q_dtype == 1 && kv_dtype == 1) sb::launch_pdl(qkv_rotate_append_kernel<bf16, bf16>, grid, dim3(256), 0, stream, p);
-  else return sb::fail("sb_qkv_rotate_append: q and cache must both be float32 or both bfloat16");
+  if (q_dtype != kv_dtype || (q_dtype != 0 && q_dtype != 1)) return sb::fail("sb_qkv_rotate_append: q and cache must both be float32 or both bfloat16");
+  const auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+  const bool vec = D % 4 == 0 && Dv % 4 == 0 && Dc % 4 == 0 && rotary_dim % 8 == 0 && partial_stride % 4 == 0 && page_stride % 4 == 0 && v_offset % 4 == 0 &&
+                   head_stride % 4 == 0 && aligned(qkv) && aligned(q_out) && aligned(pages) && aligned(cos_sin);
+  if (vec) {
+    const dim3 grid(n, (width / 4 + 127) / 128);
+    if (q_dtype == 0) sb::launch_pdl(qkv_rotate_append_vec_kernel<float, float>, grid, dim3(128), 0, stream, p);
+    else sb::launch_pdl(qkv_rotate_append_vec_kernel<bf16, bf16>, grid, dim3(128), 0, stream, p);
+  } else {
+    const dim3 grid(n, (width + 255) / 256);
+    if (q_dtype == 0) sb::launch_pdl(qkv_rotate_append_kernel<float, float>, grid, dim3(256), 0, stream, p);
+    else sb::launch_pdl(qkv_rotate_append_kernel<bf16, bf16>, grid, dim3(256), 0, stream, p);
+  }
   return sb::check_launch("sb_qkv_rotate_append");
 }
 
